@@ -1,0 +1,356 @@
+// Flash-style attention for sm_100a on tcgen05 / TMEM: the local queries of one
+// strip against the full key/value sequence, which lives as up to 8 per-peer
+// slots [B, L_slot, 2C] (K in columns [0,C), V in [C,2C), head h at columns
+// h*64..h*64+63).  The slots are read IN PLACE through one TMA descriptor per
+// slot: the own strip's fresh K/V and the peers' stale K/V are never
+// concatenated.  The same kernel serves cross-attention (one slot, 77 tokens).
+//
+// One CTA = 128 queries of one (image, head).  192 threads:
+//   warp 0      TMA producer: Q once, then a ring of {K tile, V tile} (128 tokens x 64)
+//   warp 1      tensor memory owner and tcgen05.mma issuer:
+//                 S[j&1]  = Q K_j^T        (128x128, K-major operands)
+//                 Opart[j&1] = P_j V_j     (128x64, V consumed MN-major as stored)
+//   warps 2..5  softmax: thread r owns query row r (= TMEM lane r): running max
+//               and sum, P_j -> fp16 -> swizzled shared memory, and the fp32
+//               output accumulator O (64 registers), rescaled on the fly.
+// S is double-buffered so Q K_{j+1}^T overlaps the softmax of tile j.
+//
+// Roofline: tensor cores; algorithmic FLOPs = 4 * L_q * L_kv * 64 per (image, head).
+#include "bxl_common.cuh"
+#include "bxl_host.h"
+#include "../../include/basedxl_b200.h"
+
+namespace bxl {
+
+constexpr int kAttnThreads = 192;
+constexpr int kHeadDim = 64;
+constexpr int kTileQ = 128;
+constexpr int kTileKV = 128;
+constexpr int kKvStages = 3;
+constexpr int kMaxSlots = 8;
+
+struct alignas(64) AttnParams {
+  CUtensorMap q_map;               // [C_q cols, L_q, B]
+  CUtensorMap kv_map[kMaxSlots];   // [2C cols, L_slot, B] per slot
+  int n_slots;
+  int L_q, L_slot;
+  int heads, B;
+  int v_col0;                      // column of V for head 0 (= C)
+  __half* out;                     // [B, L_q, ld_out]
+  long long out_img_stride, ld_out;
+  float scale_log2e;               // softmax scale * log2(e)
+  int* dev_status;
+};
+
+struct AttnSmem {
+  static constexpr int kQ = 0;                               // 16 KB
+  static constexpr int kK = 16384;                           // kKvStages x 16 KB
+  static constexpr int kV = kK + kKvStages * 16384;          // kKvStages x 16 KB
+  static constexpr int kP = kV + kKvStages * 16384;          // 2 x 16 KB (two 64-column halves)
+  static constexpr int kBar = kP + 32768;
+  static constexpr int kTotal = kBar + 1024 + 1024;
+};
+
+__global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid_constant__ AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + AttnSmem::kBar;
+  // barriers: q_full, kv_full[3], kv_empty[3], s_full[2], o_full[2], p_full
+  const uint32_t q_full = bar_base;
+  auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
+  auto kv_empty = [&](int s) { return bar_base + 8u * (1 + kKvStages + s); };
+  auto s_full = [&](int b) { return bar_base + 8u * (1 + 2 * kKvStages + b); };
+  auto o_full = [&](int b) { return bar_base + 8u * (3 + 2 * kKvStages + b); };
+  const uint32_t p_full = bar_base + 8u * (5 + 2 * kKvStages);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + AttnSmem::kBar + 512);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + AttnSmem::kBar + 520);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr uint32_t kTmemCols = 512;  // S0 [0,128) S1 [128,256) O0 [256,320) O1 [320,384)
+
+  const int q_tiles = (p.L_q + kTileQ - 1) / kTileQ;
+  const int qt = blockIdx.x % q_tiles;
+  const int head = (blockIdx.x / q_tiles) % p.heads;
+  const int img = blockIdx.x / (q_tiles * p.heads);
+  const int tiles_per_slot = (p.L_slot + kTileKV - 1) / kTileKV;
+  const int n_tiles = p.n_slots * tiles_per_slot;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < kKvStages; ++s) {
+      mbar_init(kv_full(s), 1);
+      mbar_init(kv_empty(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(s_full(b), 1);
+      mbar_init(o_full(b), 1);
+    }
+    mbar_init(p_full, 128);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ======================= TMA producer =======================
+    if (lane == 0) {
+      tma_prefetch_desc(&p.q_map);
+      mbar_arrive_expect_tx(q_full, 16384);
+      tma_load_3d(smem_base + AttnSmem::kQ, &p.q_map, q_full, head * kHeadDim, qt * kTileQ, img);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int slot = j / tiles_per_slot;
+        const int t0 = (j % tiles_per_slot) * kTileKV;
+        if (!mbar_wait(kv_empty(stage), phase ^ 1u, abort_flag, p.dev_status, 400)) break;
+        mbar_arrive_expect_tx(kv_full(stage), 32768);
+        tma_load_3d(smem_base + AttnSmem::kK + stage * 16384, &p.kv_map[slot], kv_full(stage), head * kHeadDim, t0, img);
+        tma_load_3d(smem_base + AttnSmem::kV + stage * 16384, &p.kv_map[slot], kv_full(stage),
+                    p.v_col0 + head * kHeadDim, t0, img);
+        if (++stage == kKvStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ======================= MMA issuer =======================
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_f16(128, 128, 0, 0);  // S = Q K^T, both K-major
+      const uint32_t idesc_o = make_idesc_f16(128, 64, 0, 1);   // O = P V, V MN-major
+      const uint64_t qdesc = make_smem_desc_sw128(smem_base + AttnSmem::kQ, 16, 1024);
+      const uint64_t pdesc0 = make_smem_desc_sw128(smem_base + AttnSmem::kP, 16, 1024);
+      const uint64_t pdesc1 = make_smem_desc_sw128(smem_base + AttnSmem::kP + 16384, 16, 1024);
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.dev_status, 500);
+      auto issue_s = [&](int j) -> bool {
+        const int st = j % kKvStages;
+        const uint32_t ph = (j / kKvStages) & 1u;
+        if (!mbar_wait(kv_full(st), ph, abort_flag, p.dev_status, 501)) return false;
+        tc_fence_after_sync();
+        const uint64_t kdesc = make_smem_desc_sw128(smem_base + AttnSmem::kK + st * 16384, 16, 1024);
+        const uint32_t d = tmem_base + (j & 1) * 128;
+#pragma unroll
+        for (int k = 0; k < kHeadDim / 16; ++k) umma_f16(d, qdesc + 2u * k, kdesc + 2u * k, idesc_s, k != 0);
+        umma_commit(s_full(j & 1));
+        return true;
+      };
+      if (ok && n_tiles > 0) ok = issue_s(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) {
+          if (!issue_s(j + 1)) break;
+        }
+        // P_j is in shared memory once all 128 softmax threads have arrived
+        if (!mbar_wait(p_full, j & 1u, abort_flag, p.dev_status, 502)) break;
+        tc_fence_after_sync();
+        const int st = j % kKvStages;
+        // V tile [128 tokens][64] as stored: MN-major B operand, 8-token groups 1 KB apart
+        const uint64_t vdesc = make_smem_desc_sw128(smem_base + AttnSmem::kV + st * 16384, 16, 1024);
+        const uint32_t d = tmem_base + 256 + (j & 1) * 64;
+#pragma unroll
+        for (int k = 0; k < kTileKV / 16; ++k) {
+          // tokens 16k..16k+15: P columns are K-major (32 B per step inside a 64-column half),
+          // V rows advance by 16 x 128 B
+          const uint64_t pd = ((k < 4) ? pdesc0 : pdesc1) + 2u * (k & 3);
+          umma_f16(d, pd, vdesc + 128u * k, idesc_o, k != 0);
+        }
+        umma_commit(kv_empty(st));
+        umma_commit(o_full(j & 1));
+      }
+    }
+  } else {
+    // ======================= softmax / output (warps 2..5) =======================
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;  // query row inside the tile == TMEM lane
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    float o_acc[kHeadDim];
+#pragma unroll
+    for (int i = 0; i < kHeadDim; ++i) o_acc[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+    uint8_t* p_smem = smem_gen + AttnSmem::kP;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int t0 = (j % tiles_per_slot) * kTileKV;
+      const int valid = min(kTileKV, p.L_slot - t0);
+      if (!mbar_wait(s_full(j & 1), (j >> 1) & 1u, abort_flag, p.dev_status, 600)) {
+        ok = false;
+        break;
+      }
+      __syncwarp();
+      tc_fence_after_sync();
+      const uint32_t s_addr = t_lane + (j & 1) * 128;
+      // pass 1: row maximum
+      float m_tile = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(s_addr + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (c * 32 + i < valid) m_tile = fmaxf(m_tile, __uint_as_float(v[i]));
+      }
+      const float m_new = fmaxf(m_run, m_tile * p.scale_log2e);
+      const float alpha = exp2f(m_run - m_new);  // exp2f(-inf) = 0 on the first tile
+      // the previous tile's P V product: frees the P buffer and delivers Opart_{j-1}
+      if (j > 0) {
+        if (!mbar_wait(o_full((j - 1) & 1), ((j - 1) >> 1) & 1u, abort_flag, p.dev_status, 601)) {
+          ok = false;
+          break;
+        }
+        __syncwarp();
+        tc_fence_after_sync();
+        const uint32_t o_addr = t_lane + 256 + ((j - 1) & 1) * 64;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(o_addr + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha_prev + __uint_as_float(v[i]);
+        }
+      }
+      // pass 2: P = exp2(S*scale - m), row sum, fp16 into swizzled shared memory
+      float l_tile = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(s_addr + c * 32, v);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int col = c * 32 + 2 * i;
+          float p0 = (col < valid) ? exp2f(__uint_as_float(v[2 * i]) * p.scale_log2e - m_new) : 0.f;
+          float p1 = (col + 1 < valid) ? exp2f(__uint_as_float(v[2 * i + 1]) * p.scale_log2e - m_new) : 0.f;
+          const __half2 h = __floats2half2_rn(p0, p1);
+          // the row sum uses the rounded values the tensor core will see
+          const float2 hr = __half22float2(h);
+          l_tile += hr.x + hr.y;
+          packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        // 32 columns = 4 chunks of 16 B; half = c/2, chunk index inside the half = (c%2)*4 + q
+        uint8_t* half_base = p_smem + (c >> 1) * 16384;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t off = sw128_offset(row, (c & 1) * 4 + q);
+          *reinterpret_cast<uint4*>(half_base + off) =
+              make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+        }
+      }
+      l_run = l_run * alpha + l_tile;
+      m_run = m_new;
+      alpha_prev = alpha;
+      // publish P_j (generic-proxy writes -> async proxy) and release S[j&1]
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(p_full);
+    }
+    if (ok && n_tiles > 0) {
+      const int j = n_tiles - 1;
+      if (mbar_wait(o_full(j & 1), (j >> 1) & 1u, abort_flag, p.dev_status, 602)) {
+        __syncwarp();
+        tc_fence_after_sync();
+        const uint32_t o_addr = t_lane + 256 + (j & 1) * 64;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(o_addr + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha_prev + __uint_as_float(v[i]);
+        }
+        const int q_row = qt * kTileQ + row;
+        if (q_row < p.L_q) {
+          const float inv_l = 1.f / l_run;
+          __half* dst = p.out + (long long)img * p.out_img_stride + (long long)q_row * p.ld_out + head * kHeadDim;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            uint4 u;
+            __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              h[i] = __floats2half2_rn(o_acc[q * 8 + 2 * i] * inv_l, o_acc[q * 8 + 2 * i + 1] * inv_l);
+            *reinterpret_cast<uint4*>(dst + q * 8) = u;
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown ---------------------------------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    const unsigned long long t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace bxl
+
+using namespace bxl;
+
+extern "C" int bxl_attn_fwd_f16(const void* q, long long q_img_stride, long long ld_q, const void* const* kv_slots,
+                                int n_slots, long long kv_img_stride, long long ld_kv, int v_col0, void* out,
+                                long long out_img_stride, long long ld_out, int B, int heads, int L_q, int L_slot,
+                                float scale, void* stream) {
+  if (!q || !kv_slots || !out) return fail(kErrInvalidArg, "bxl_attn_fwd_f16: null pointer");
+  if (n_slots < 1 || n_slots > kMaxSlots) return fail(kErrInvalidArg, "bxl_attn_fwd_f16: n_slots=%d (1..%d)", n_slots, kMaxSlots);
+  if (B <= 0 || heads <= 0 || L_q <= 0 || L_slot <= 0) return fail(kErrInvalidArg, "bxl_attn_fwd_f16: non-positive extent");
+  if (ld_q % 8 || ld_kv % 8 || ld_out % 8 || q_img_stride % 8 || kv_img_stride % 8 || out_img_stride % 8 || v_col0 % 8)
+    return fail(kErrInvalidArg, "bxl_attn_fwd_f16: strides must be multiples of 8 elements");
+  if (ld_q < heads * kHeadDim || ld_out < heads * kHeadDim || ld_kv < v_col0 + heads * kHeadDim || v_col0 < heads * kHeadDim)
+    return fail(kErrInvalidArg, "bxl_attn_fwd_f16: row strides too small for %d heads of 64", heads);
+  if ((reinterpret_cast<uintptr_t>(q) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u))
+    return fail(kErrInvalidArg, "bxl_attn_fwd_f16: q/out must be 16-byte aligned");
+  int* st = device_status_ptr();
+  if (!st) return fail(kErrCuda, "bxl_attn_fwd_f16: no device status word");
+  AttnParams p;
+  memset(&p, 0, sizeof(p));
+  {
+    uint64_t dims[3] = {(uint64_t)(heads * kHeadDim), (uint64_t)L_q, (uint64_t)B};
+    uint64_t str[2] = {(uint64_t)ld_q * 2, (uint64_t)q_img_stride * 2};
+    uint32_t box[3] = {kHeadDim, kTileQ, 1};
+    if (int rc = encode_tmap_f16(&p.q_map, q, 3, dims, str, box)) return rc;
+  }
+  for (int s = 0; s < kMaxSlots; ++s) {
+    const void* base = kv_slots[s < n_slots ? s : 0];
+    if (!base) return fail(kErrInvalidArg, "bxl_attn_fwd_f16: slot %d null", s);
+    uint64_t dims[3] = {(uint64_t)(v_col0 + heads * kHeadDim), (uint64_t)L_slot, (uint64_t)B};
+    uint64_t str[2] = {(uint64_t)ld_kv * 2, (uint64_t)kv_img_stride * 2};
+    uint32_t box[3] = {kHeadDim, kTileKV, 1};
+    if (int rc = encode_tmap_f16(&p.kv_map[s], base, 3, dims, str, box)) return rc;
+  }
+  p.n_slots = n_slots, p.L_q = L_q, p.L_slot = L_slot, p.heads = heads, p.B = B, p.v_col0 = v_col0;
+  p.out = static_cast<__half*>(out);
+  p.out_img_stride = out_img_stride, p.ld_out = ld_out;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.dev_status = st;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (int rc = check_cuda(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::kTotal),
+                            "cudaFuncSetAttribute(attention)"))
+      return rc;
+    configured[dev] = true;
+  }
+  const int q_tiles = (L_q + kTileQ - 1) / kTileQ;
+  attention_kernel<<<q_tiles * heads * B, kAttnThreads, AttnSmem::kTotal, (cudaStream_t)stream>>>(p);
+  return check_cuda(cudaGetLastError(), "attention_kernel launch");
+}

@@ -1,0 +1,32 @@
+// Host-side plumbing shared by the C-ABI entry points: error reporting, the
+// device status word, and TMA descriptor encoding through the driver entry
+// point (the library does not link against libcuda).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace bxl {
+
+// status codes returned over the C ABI (0 = ok, negative = error)
+enum : int {
+  kOk = 0,
+  kErrInvalidArg = -1,
+  kErrCuda = -2,
+  kErrUnsupported = -3,
+  kErrDevice = -4,   // a kernel recorded a failure in the device status word
+  kErrTooLarge = -5,
+};
+
+int fail(int code, const char* fmt, ...);          // records the message, returns code
+int check_cuda(cudaError_t e, const char* what);   // kOk or kErrCuda (+ message)
+int* device_status_ptr();                          // per-device status word (3 ints), nullptr on failure
+
+// 16-bit (fp16) tiled tensor map with 128-byte swizzle and zero fill.
+// dims/box: innermost first.  strides_bytes: rank-1 entries for dims 1..rank-1.
+int encode_tmap_f16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                    const uint32_t* box);
+
+int sm_count();
+
+}  // namespace bxl

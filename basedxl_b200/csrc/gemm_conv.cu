@@ -1,0 +1,567 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a, with two front ends:
+//
+//   * plain / split-operand GEMM   C[M,N] = sum_s A_s[M,K] * B_s  (+bias, +residual)
+//   * halo-aware implicit-GEMM 3x3 convolution on an H-strip in NHWC, whose A
+//     tiles are gathered by TMA row by row from three sources: the fresh local
+//     strip and the (stale) boundary rows of the strips above and below.
+//
+// Roles inside a CTA of 192 threads (one CTA per SM, tiles strided by grid):
+//   warp 0      TMA producer: fills a ring of {A 128x64, B BNx64} fp16 stages
+//   warp 1      allocates tensor memory and issues tcgen05.mma (one lane)
+//   warps 2..5  epilogue: tcgen05.ld the fp32 accumulator, add bias/residual,
+//               convert and store; runs while the next tile's mainloop fills the
+//               other accumulator buffer (two TMEM buffers of BN columns)
+//
+// Roofline: tensor cores.  Algorithmic FLOPs per tile = 2*128*BN*K.
+#include "bxl_common.cuh"
+#include "bxl_host.h"
+#include "../../include/basedxl_b200.h"
+
+namespace bxl {
+
+constexpr int kBM = 128;           // tile rows (= TMEM lanes, UMMA M)
+constexpr int kBK = 64;            // K per stage: 64 fp16 = one 128-byte swizzle row
+constexpr int kUmmaK = 16;         // K of one tcgen05.mma.kind::f16
+constexpr int kGemmThreads = 192;
+constexpr int kMaxSeg = 3;
+
+struct alignas(64) GemmParams {
+  CUtensorMap a_map[kMaxSeg];  // GEMM: A of each segment.  conv: body, top halo, bottom halo
+  CUtensorMap b_map[kMaxSeg];  // GEMM: B of each segment.  conv: [0] = packed weights
+  // problem
+  int M, N, K;                 // conv: M = B*H_out*W_out (unused), N = C_out, K = 9*C_in
+  int nseg;                    // GEMM segments (1, or 3 for the split-operand product)
+  int b_kn;                    // B given as [K,N] row-major (MN-major operand) instead of [N,K]
+  // epilogue
+  const __half* bias;          // [N] or null
+  const __half* bias_rows;     // conv only: [B][N] per-image bias (time embedding) or null
+  const __half* residual;      // [M][ldr] or null
+  long long ldr;
+  void* C;
+  long long ldc;
+  int out_f32;
+  // conv geometry
+  int cB, cHin, cW, cCin, cStride, cHout, cWout;
+  int tw, th;                  // tile = th rows x tw columns of output pixels (th*tw = 128)
+  int tiles_x, tiles_y;        // tiles per image
+  int has_top, has_bot;
+  int* dev_status;
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int kABytes = kBM * kBK * 2;            // 16 KB
+  static constexpr int kBBytes = BN * kBK * 2;             // 16 / 32 KB
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kBarBytes = 1024;
+  static constexpr int kTotal = kStages * kStageBytes + kBarBytes + 1024;  // + alignment slack
+};
+
+template <int BN, bool kConv>
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid_constant__ GemmParams p) {
+  using S = GemmSmem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + S::kStages * S::kStageBytes;
+  // barrier layout (8 bytes each): full[kStages], empty[kStages], tfull[2], tempty[2]
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (S::kStages + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * S::kStages + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * S::kStages + 2 + a); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + S::kStages * S::kStageBytes + 512);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + S::kStages * S::kStageBytes + 520);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr uint32_t kTmemCols = 2 * BN;  // 256 or 512: a power of two >= 32
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // ---- tile enumeration ------------------------------------------------------
+  const int tiles_n = (p.N + BN - 1) / BN;
+  int tiles_m;
+  if (kConv) tiles_m = p.cB * p.tiles_y * p.tiles_x;
+  else tiles_m = (p.M + kBM - 1) / kBM;
+  const int num_tiles = tiles_m * tiles_n;
+  const int kb_per_seg = kConv ? 9 * (p.cCin / kBK) : (p.K + kBK - 1) / kBK;
+  const int num_kb = kConv ? kb_per_seg : kb_per_seg * p.nseg;
+
+  if (warp == 0) {
+    // ======================= TMA producer =======================
+    if (lane == 0) {
+      for (int s = 0; s < kMaxSeg; ++s) {
+        tma_prefetch_desc(&p.a_map[s]);
+        tma_prefetch_desc(&p.b_map[s]);
+      }
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int tm = tile % tiles_m;
+        const int tn = tile / tiles_m;
+        const int n0 = tn * BN;
+        int img = 0, y0 = 0, x0 = 0;
+        if (kConv) {
+          const int per_img = p.tiles_y * p.tiles_x;
+          img = tm / per_img;
+          const int r = tm % per_img;
+          y0 = (r / p.tiles_x) * p.th;
+          x0 = (r % p.tiles_x) * p.tw;
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.dev_status, 100)) {
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = smem_base + stage * S::kStageBytes;
+          const uint32_t b_dst = a_dst + S::kABytes;
+          mbar_arrive_expect_tx(full_bar(stage), S::kStageBytes);
+          if (kConv) {
+            const int cchunks = p.cCin / kBK;
+            const int tap = kb / cchunks;
+            const int c0 = (kb % cchunks) * kBK;
+            const int ky = tap / 3, kx = tap % 3;
+            // input column of output column ox: stride*ox + kx - 1, addressed as
+            // (parity, half-column) = ((kx-1) mod stride, ox + floor((kx-1)/stride))
+            int par = 0, xoff = kx - 1;
+            if (p.cStride == 2) {
+              par = (kx == 1) ? 0 : 1;
+              xoff = (kx == 0) ? -1 : 0;
+            }
+            for (int t = 0; t < p.th; ++t) {
+              const int r_in = p.cStride * (y0 + t) + ky - 1;
+              const uint32_t dst = a_dst + t * p.tw * 128;
+              if (r_in == -1 && p.has_top) {
+                tma_load_5d(dst, &p.a_map[1], full_bar(stage), c0, par, x0 + xoff, 0, img);
+              } else if (r_in == p.cHin && p.has_bot) {
+                tma_load_5d(dst, &p.a_map[2], full_bar(stage), c0, par, x0 + xoff, 0, img);
+              } else {
+                // rows outside [0, H) are zero-filled by the copy engine
+                tma_load_5d(dst, &p.a_map[0], full_bar(stage), c0, par, x0 + xoff, r_in, img);
+              }
+            }
+            tma_load_2d(b_dst, &p.b_map[0], full_bar(stage), kb * kBK, n0);
+          } else {
+            const int seg = kb / kb_per_seg;
+            const int k0 = (kb % kb_per_seg) * kBK;
+            tma_load_2d(a_dst, &p.a_map[seg], full_bar(stage), k0, tm * kBM);
+            if (p.b_kn) {
+              // B[K,N]: one 64(n) x 64(k) box per 64 output columns
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(b_dst + j * 8192, &p.b_map[seg], full_bar(stage), n0 + j * 64, k0);
+            } else {
+              tma_load_2d(b_dst, &p.b_map[seg], full_bar(stage), k0, n0);
+            }
+          }
+          if (++stage == S::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ======================= MMA issuer =======================
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(kBM, BN, 0, (!kConv && p.b_kn) ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1u;
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.dev_status, 200)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.dev_status, 201)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_base + stage * S::kStageBytes;
+          const uint32_t b_addr = a_addr + S::kABytes;
+          const uint64_t adesc = make_smem_desc_sw128(a_addr, 16, 1024);
+          if (!kConv && p.b_kn) {
+            // MN-major B: 64-column chunks 8 KB apart (LBO), 8-row k-groups 1 KB apart (SBO)
+            const uint64_t bdesc = make_smem_desc_sw128(b_addr, 8192, 1024);
+#pragma unroll
+            for (int k = 0; k < kBK / kUmmaK; ++k)
+              umma_f16(d_tmem, adesc + 2u * k, bdesc + 128u * k, idesc, (kb | k) != 0);
+          } else {
+            const uint64_t bdesc = make_smem_desc_sw128(b_addr, 16, 1024);
+#pragma unroll
+            for (int k = 0; k < kBK / kUmmaK; ++k)
+              umma_f16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0);
+          }
+          umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+          if (++stage == S::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit(tfull_bar(acc));
+      }
+    }
+  } else {
+    // ======================= epilogue (warps 2..5) =======================
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may access
+    const int row_in_tile = quarter * 32 + lane;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1u;
+      const int tm = tile % tiles_m;
+      const int tn = tile / tiles_m;
+      const int n0 = tn * BN;
+      long long out_row = -1;  // row index into C / residual, -1 = not stored
+      int img = 0;
+      if (kConv) {
+        const int per_img = p.tiles_y * p.tiles_x;
+        img = tm / per_img;
+        const int r = tm % per_img;
+        const int oy = (r / p.tiles_x) * p.th + row_in_tile / p.tw;
+        const int ox = (r % p.tiles_x) * p.tw + row_in_tile % p.tw;
+        if (oy < p.cHout && ox < p.cWout) out_row = (static_cast<long long>(img) * p.cHout + oy) * p.cWout + ox;
+      } else {
+        const int m = tm * kBM + row_in_tile;
+        if (m < p.M) out_row = m;
+      }
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.dev_status, 300)) break;
+      tc_fence_after_sync();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_row + c * 32, v);
+        tmem_ld_wait();
+        const int nb = n0 + c * 32;
+        if (out_row >= 0 && nb < p.N) {
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          const bool fullw = (nb + 32 <= p.N);
+          if (p.bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (fullw || nb + j < p.N) f[j] += __half2float(p.bias[nb + j]);
+          }
+          if (kConv && p.bias_rows) {
+            const __half* br = p.bias_rows + static_cast<long long>(img) * p.N;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (fullw || nb + j < p.N) f[j] += __half2float(br[nb + j]);
+          }
+          if (p.residual) {
+            const __half* rr = p.residual + out_row * p.ldr + nb;
+            if (fullw) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 u = *reinterpret_cast<const uint4*>(rr + q * 8);
+                const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 g = __half22float2(h[j]);
+                  f[q * 8 + 2 * j] += g.x;
+                  f[q * 8 + 2 * j + 1] += g.y;
+                }
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (nb + j < p.N) f[j] += __half2float(rr[j]);
+            }
+          }
+          if (p.out_f32) {
+            float* cr = static_cast<float*>(p.C) + out_row * p.ldc + nb;
+            if (fullw) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<float4*>(cr + q * 4) = make_float4(f[q * 4], f[q * 4 + 1], f[q * 4 + 2], f[q * 4 + 3]);
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (nb + j < p.N) cr[j] = f[j];
+            }
+          } else {
+            __half* cr = static_cast<__half*>(p.C) + out_row * p.ldc + nb;
+            if (fullw) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 u;
+                __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(f[q * 8 + 2 * j], f[q * 8 + 2 * j + 1]);
+                *reinterpret_cast<uint4*>(cr + q * 8) = u;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (nb + j < p.N) cr[j] = __float2half_rn(f[j]);
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  // ---- teardown ---------------------------------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies that may still be in flight time to land before the CTA's
+    // shared memory is released
+    const unsigned long long t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------
+template <int BN, bool kConv>
+static int launch(const GemmParams& p, int num_tiles, cudaStream_t stream) {
+  using S = GemmSmem<BN>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (int rc = check_cuda(cudaFuncSetAttribute(gemm_conv_kernel<BN, kConv>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 S::kTotal),
+                            "cudaFuncSetAttribute(gemm)"))
+      return rc;
+    configured[dev] = true;
+  }
+  int grid = sm_count();
+  if (grid > num_tiles) grid = num_tiles;
+  if (grid < 1) grid = 1;
+  gemm_conv_kernel<BN, kConv><<<grid, kGemmThreads, S::kTotal, stream>>>(p);
+  return check_cuda(cudaGetLastError(), "gemm_conv_kernel launch");
+}
+
+// tile width: fewest wasted columns, ties to the wider tile
+static int pick_bn(int N) {
+  const int t128 = (N + 127) / 128 * 128, t256 = (N + 255) / 256 * 256;
+  return (t256 <= t128) ? 256 : 128;
+}
+
+static int aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace bxl
+
+using namespace bxl;
+
+extern "C" int bxl_gemm_f16(const void* A, long long lda, const void* B, long long ldb, int b_is_kn, const void* bias,
+                            const void* residual, long long ldr, void* C, long long ldc, int out_f32, int M, int N, int K,
+                            void* stream) {
+  if (!A || !B || !C) return fail(kErrInvalidArg, "bxl_gemm_f16: null operand");
+  if (M <= 0 || N <= 0 || K <= 0) return fail(kErrInvalidArg, "bxl_gemm_f16: non-positive extent M=%d N=%d K=%d", M, N, K);
+  if (lda % 8 || ldb % 8) return fail(kErrInvalidArg, "bxl_gemm_f16: lda/ldb must be multiples of 8 elements");
+  if (!aligned16(A) || !aligned16(B) || !aligned16(C) || (residual && !aligned16(residual)))
+    return fail(kErrInvalidArg, "bxl_gemm_f16: operands must be 16-byte aligned");
+  if (ldc % (out_f32 ? 4 : 8) || (residual && ldr % 8))
+    return fail(kErrInvalidArg, "bxl_gemm_f16: ldc/ldr must keep rows 16-byte aligned");
+  if (lda < K || (b_is_kn ? ldb < N : ldb < K) || ldc < N) return fail(kErrInvalidArg, "bxl_gemm_f16: leading dimension too small");
+  int* st = device_status_ptr();
+  if (!st) return fail(kErrCuda, "bxl_gemm_f16: no device status word");
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  const int BN = pick_bn(N);
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    uint64_t str[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {kBK, kBM};
+    if (int rc = encode_tmap_f16(&p.a_map[0], A, 2, dims, str, box)) return rc;
+  }
+  if (b_is_kn) {
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)K};
+    uint64_t str[1] = {(uint64_t)ldb * 2};
+    uint32_t box[2] = {64, kBK};
+    if (int rc = encode_tmap_f16(&p.b_map[0], B, 2, dims, str, box)) return rc;
+  } else {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+    uint64_t str[1] = {(uint64_t)ldb * 2};
+    uint32_t box[2] = {kBK, (uint32_t)BN};
+    if (int rc = encode_tmap_f16(&p.b_map[0], B, 2, dims, str, box)) return rc;
+  }
+  for (int s = 1; s < kMaxSeg; ++s) {
+    p.a_map[s] = p.a_map[0];
+    p.b_map[s] = p.b_map[0];
+  }
+  p.M = M, p.N = N, p.K = K, p.nseg = 1, p.b_kn = b_is_kn ? 1 : 0;
+  p.bias = static_cast<const __half*>(bias);
+  p.residual = static_cast<const __half*>(residual);
+  p.ldr = ldr, p.C = C, p.ldc = ldc, p.out_f32 = out_f32 ? 1 : 0;
+  p.dev_status = st;
+  const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
+  return BN == 256 ? launch<256, false>(p, tiles, (cudaStream_t)stream) : launch<128, false>(p, tiles, (cudaStream_t)stream);
+}
+
+// ---- split-operand product of fp32 matrices ---------------------------------------
+namespace bxl {
+// x = hi + lo with hi = fp16(x), lo = fp16(x - hi): 22 significant bits kept.
+__global__ void split_f32_kernel(const float* __restrict__ x, __half* __restrict__ hi, __half* __restrict__ lo, long long n4) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(x)[i];
+    const __half h0 = __float2half_rn(v.x), h1 = __float2half_rn(v.y), h2 = __float2half_rn(v.z), h3 = __float2half_rn(v.w);
+    __half2 hh[2] = {__halves2half2(h0, h1), __halves2half2(h2, h3)};
+    __half2 ll[2] = {__floats2half2_rn(v.x - __half2float(h0), v.y - __half2float(h1)),
+                     __floats2half2_rn(v.z - __half2float(h2), v.w - __half2float(h3))};
+    reinterpret_cast<uint2*>(hi)[i] = *reinterpret_cast<uint2*>(hh);
+    reinterpret_cast<uint2*>(lo)[i] = *reinterpret_cast<uint2*>(ll);
+  }
+}
+}  // namespace bxl
+
+extern "C" long long bxl_gemm_split_workspace_bytes(int M, int N, int K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  return 2ll * 2 * ((long long)M * K + (long long)K * N) + 1024;
+}
+
+extern "C" int bxl_gemm_split_f32(const float* A, const float* B, float* C, int M, int N, int K, void* workspace,
+                                  long long workspace_bytes, void* stream) {
+  if (!A || !B || !C || !workspace) return fail(kErrInvalidArg, "bxl_gemm_split_f32: null pointer");
+  if (M <= 0 || N <= 0 || K <= 0) return fail(kErrInvalidArg, "bxl_gemm_split_f32: non-positive extent");
+  if (K % 8 || N % 8) return fail(kErrInvalidArg, "bxl_gemm_split_f32: K and N must be multiples of 8");
+  if (!aligned16(A) || !aligned16(B) || !aligned16(C) || !aligned16(workspace))
+    return fail(kErrInvalidArg, "bxl_gemm_split_f32: pointers must be 16-byte aligned");
+  if (workspace_bytes < bxl_gemm_split_workspace_bytes(M, N, K)) return fail(kErrTooLarge, "bxl_gemm_split_f32: workspace too small");
+  int* st = device_status_ptr();
+  if (!st) return fail(kErrCuda, "bxl_gemm_split_f32: no device status word");
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long na = (long long)M * K, nb = (long long)K * N;
+  __half* a_hi = static_cast<__half*>(workspace);
+  __half* a_lo = a_hi + na;
+  __half* b_hi = a_lo + na;
+  __half* b_lo = b_hi + nb;
+  const int blocks = sm_count() * 8;
+  split_f32_kernel<<<blocks, 256, 0, s>>>(A, a_hi, a_lo, na / 4);
+  split_f32_kernel<<<blocks, 256, 0, s>>>(B, b_hi, b_lo, nb / 4);
+  if (int rc = check_cuda(cudaGetLastError(), "split_f32_kernel launch")) return rc;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  const int BN = pick_bn(N);
+  // C = A_hi*B_hi + A_hi*B_lo + A_lo*B_hi, one fp32 accumulator
+  const __half* as[3] = {a_hi, a_hi, a_lo};
+  const __half* bs[3] = {b_hi, b_lo, b_hi};
+  for (int i = 0; i < 3; ++i) {
+    uint64_t ad[2] = {(uint64_t)K, (uint64_t)M};
+    uint64_t astr[1] = {(uint64_t)K * 2};
+    uint32_t abox[2] = {kBK, kBM};
+    if (int rc = encode_tmap_f16(&p.a_map[i], as[i], 2, ad, astr, abox)) return rc;
+    uint64_t bd[2] = {(uint64_t)N, (uint64_t)K};
+    uint64_t bstr[1] = {(uint64_t)N * 2};
+    uint32_t bbox[2] = {64, kBK};
+    if (int rc = encode_tmap_f16(&p.b_map[i], bs[i], 2, bd, bstr, bbox)) return rc;
+  }
+  p.M = M, p.N = N, p.K = K, p.nseg = 3, p.b_kn = 1;
+  p.C = C, p.ldc = N, p.out_f32 = 1;
+  p.dev_status = st;
+  const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
+  return BN == 256 ? launch<256, false>(p, tiles, s) : launch<128, false>(p, tiles, s);
+}
+
+// ---- convolution --------------------------------------------------------------------
+namespace bxl {
+// [C_out][C_in][3][3] -> [C_out][ky][kx][C_in]  (K index = tap*C_in + c)
+__global__ void conv_weight_pack_kernel(const __half* __restrict__ w, __half* __restrict__ out, int cout, int cin) {
+  const long long total = (long long)cout * cin * 9;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int c = i % cin;
+    const int tap = (i / cin) % 9;
+    const int o = i / (9ll * cin);
+    out[i] = w[((long long)o * cin + c) * 9 + tap];
+  }
+}
+}  // namespace bxl
+
+extern "C" int bxl_conv_weight_pack_f16(const void* w_oihw, void* w_packed, int c_out, int c_in, void* stream) {
+  if (!w_oihw || !w_packed || c_out <= 0 || c_in <= 0) return fail(kErrInvalidArg, "bxl_conv_weight_pack_f16: bad argument");
+  conv_weight_pack_kernel<<<sm_count() * 4, 256, 0, (cudaStream_t)stream>>>(static_cast<const __half*>(w_oihw),
+                                                                             static_cast<__half*>(w_packed), c_out, c_in);
+  return check_cuda(cudaGetLastError(), "conv_weight_pack_kernel launch");
+}
+
+extern "C" int bxl_conv3x3_halo_f16(const void* x, long long x_img_stride, const void* top, const void* bot,
+                                    long long halo_img_stride, const void* w_packed, const void* bias, const void* bias_rows,
+                                    const void* residual, void* y, int B, int C_in, int C_out, int H_in, int W, int stride,
+                                    void* stream) {
+  if (!x || !w_packed || !y) return fail(kErrInvalidArg, "bxl_conv3x3_halo_f16: null operand");
+  if (B <= 0 || H_in <= 0 || W <= 0) return fail(kErrInvalidArg, "bxl_conv3x3_halo_f16: non-positive extent");
+  if (stride != 1 && stride != 2) return fail(kErrUnsupported, "bxl_conv3x3_halo_f16: stride %d (1 or 2 supported)", stride);
+  if (C_in % 64) return fail(kErrUnsupported, "bxl_conv3x3_halo_f16: C_in=%d must be a multiple of 64 (use the direct kernel)", C_in);
+  if (C_out % 8) return fail(kErrUnsupported, "bxl_conv3x3_halo_f16: C_out=%d must be a multiple of 8", C_out);
+  if (W % stride || H_in % stride) return fail(kErrInvalidArg, "bxl_conv3x3_halo_f16: H and W must be multiples of the stride");
+  if (!aligned16(x) || !aligned16(w_packed) || !aligned16(y) || (top && !aligned16(top)) || (bot && !aligned16(bot)) ||
+      (residual && !aligned16(residual)))
+    return fail(kErrInvalidArg, "bxl_conv3x3_halo_f16: pointers must be 16-byte aligned");
+  if (x_img_stride % 8 || halo_img_stride % 8) return fail(kErrInvalidArg, "bxl_conv3x3_halo_f16: image strides must be multiples of 8");
+  int* st = device_status_ptr();
+  if (!st) return fail(kErrCuda, "bxl_conv3x3_halo_f16: no device status word");
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  const int Wh = W / stride;  // half-columns (== output width)
+  const int H_out = H_in / stride, W_out = W / stride;
+  int tw = 128;
+  while (tw > W_out && tw > 8) tw >>= 1;  // tile width: power of two <= W_out, >= 8
+  const int th = 128 / tw;
+  // 5-D view [C, stride, W/stride, H, B] of an NHWC strip
+  auto enc = [&](CUtensorMap* m, const void* base, int rows, long long img_stride) {
+    uint64_t dims[5] = {(uint64_t)C_in, (uint64_t)stride, (uint64_t)Wh, (uint64_t)rows, (uint64_t)B};
+    uint64_t str[4] = {(uint64_t)C_in * 2, (uint64_t)stride * C_in * 2, (uint64_t)W * C_in * 2, (uint64_t)img_stride * 2};
+    uint32_t box[5] = {kBK, 1, (uint32_t)tw, 1, 1};
+    return encode_tmap_f16(m, base, 5, dims, str, box);
+  };
+  if (int rc = enc(&p.a_map[0], x, H_in, x_img_stride)) return rc;
+  if (int rc = enc(&p.a_map[1], top ? top : x, 1, top ? halo_img_stride : x_img_stride)) return rc;
+  if (int rc = enc(&p.a_map[2], bot ? bot : x, 1, bot ? halo_img_stride : x_img_stride)) return rc;
+  const int K = 9 * C_in;
+  const int BN = pick_bn(C_out);
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)C_out};
+    uint64_t str[1] = {(uint64_t)K * 2};
+    uint32_t box[2] = {kBK, (uint32_t)BN};
+    if (int rc = encode_tmap_f16(&p.b_map[0], w_packed, 2, dims, str, box)) return rc;
+  }
+  p.b_map[1] = p.b_map[0];
+  p.b_map[2] = p.b_map[0];
+  p.M = B * H_out * W_out, p.N = C_out, p.K = K, p.nseg = 1, p.b_kn = 0;
+  p.bias = static_cast<const __half*>(bias);
+  p.bias_rows = static_cast<const __half*>(bias_rows);
+  p.residual = static_cast<const __half*>(residual);
+  p.ldr = C_out, p.C = y, p.ldc = C_out, p.out_f32 = 0;
+  p.cB = B, p.cHin = H_in, p.cW = W, p.cCin = C_in, p.cStride = stride, p.cHout = H_out, p.cWout = W_out;
+  p.tw = tw, p.th = th;
+  p.tiles_x = (W_out + tw - 1) / tw, p.tiles_y = (H_out + th - 1) / th;
+  p.has_top = top ? 1 : 0, p.has_bot = bot ? 1 : 0;
+  p.dev_status = st;
+  const int tiles = B * p.tiles_x * p.tiles_y * ((C_out + BN - 1) / BN);
+  return BN == 256 ? launch<256, true>(p, tiles, (cudaStream_t)stream) : launch<128, true>(p, tiles, (cudaStream_t)stream);
+}

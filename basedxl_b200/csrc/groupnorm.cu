@@ -1,0 +1,245 @@
+// GroupNorm on an NHWC H-strip with cross-strip (possibly stale) moments, fused
+// with the SiLU that follows it in the residual blocks.
+//
+//   pass 1  groupnorm_stats_kernel: per-(image, group) first and second raw
+//           moments of the local strip, fp32.  Every CTA reduces a slab of
+//           pixels; per-CTA partials go to scratch, and the last CTA to finish
+//           (a self-resetting ticket counter in scratch) folds them, in fixed
+//           order, into the moments buffer the strip publishes to its peers.
+//   pass 2  groupnorm_apply_kernel: combines the fresh moments with the peers'
+//           buffers (sync: average of all; stale: average of the stale buffers
+//           plus the own fresh-minus-stale correction), forms the variance with
+//           the negative-variance fallback and the local-count Bessel factor,
+//           and writes y = (x - mean) * rstd * gamma + beta, optionally
+//           y * sigmoid(y).
+//
+// Roofline: HBM.  Algorithmic bytes = read x + write y (2 * numel * 2 B); pass 1
+// re-reads x, which for the strip sizes of this workload is served by L2.
+#include "bxl_common.cuh"
+#include "bxl_host.h"
+#include "../../include/basedxl_b200.h"
+
+namespace bxl {
+
+constexpr int kGnMaxParts = 128;   // per-image partial slabs
+constexpr int kGnMaxGroups = 64;
+constexpr int kGnMaxC = 4096;
+
+// scratch layout: [0] ticket counter (int, kept at 0 between launches), then
+// partials [B][parts][G][2] floats starting at byte 256
+__global__ void __launch_bounds__(512) groupnorm_stats_kernel(const __half* __restrict__ x, long long img_stride, int HW,
+                                                              int C, int G, int parts, float* __restrict__ partials,
+                                                              int* __restrict__ ticket, float* __restrict__ moments, int B) {
+  extern __shared__ float s_ch[];  // [2][C] per-channel sum / sum of squares
+  __shared__ int s_last;
+  const int vecs = C / 8;               // 16-byte vectors per pixel
+  const int rows = blockDim.x / vecs;   // pixels handled per sweep
+  const int part = blockIdx.x, img = blockIdx.y;
+  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) s_ch[i] = 0.f;
+  __syncthreads();
+  const int v = threadIdx.x % vecs, r = threadIdx.x / vecs;
+  float s1[8], s2[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s1[j] = s2[j] = 0.f;
+  if (r < rows) {
+    const int per = (HW + parts - 1) / parts;
+    const int p0 = part * per, p1 = min(HW, p0 + per);
+    const __half* base = x + (long long)img * img_stride + (long long)v * 8;
+    for (int pix = p0 + r; pix < p1; pix += rows) {
+      const uint4 u = *reinterpret_cast<const uint4*>(base + (long long)pix * C);
+      const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h[j]);
+        s1[2 * j] += f.x, s2[2 * j] += f.x * f.x;
+        s1[2 * j + 1] += f.y, s2[2 * j + 1] += f.y * f.y;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      atomicAdd(&s_ch[v * 8 + j], s1[j]);
+      atomicAdd(&s_ch[C + v * 8 + j], s2[j]);
+    }
+  }
+  __syncthreads();
+  const int cpg = C / G;
+  if (threadIdx.x < 2 * G) {
+    const int g = threadIdx.x % G, which = threadIdx.x / G;
+    float acc = 0.f;
+    for (int c = 0; c < cpg; ++c) acc += s_ch[which * C + g * cpg + c];
+    partials[(((long long)img * parts + part) * G + g) * 2 + which] = acc;
+  }
+  // last CTA of the whole grid folds the partials
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int total = gridDim.x * gridDim.y;
+    const int t = atomicAdd(ticket, 1);
+    s_last = (t == total - 1);
+    if (s_last) *ticket = 0;  // ready for the next launch on this stream
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const float inv_n = 1.f / (float)((long long)cpg * HW);
+  for (int i = threadIdx.x; i < B * G * 2; i += blockDim.x) {
+    const int which = i % 2, g = (i / 2) % G, b = i / (2 * G);
+    float acc = 0.f;
+    for (int q = 0; q < parts; ++q) acc += __ldcg(&partials[(((long long)b * parts + q) * G + g) * 2 + which]);
+    // published layout [2][B][G]: first moments, then second moments
+    moments[((long long)which * B + b) * G + g] = acc * inv_n;
+  }
+}
+
+struct GnPeers {
+  const float* ptr[8];
+};
+
+// mode: 0 local, 1 sync (average of peers; own slot already holds the fresh moments),
+//       2 stale (average of peers + fresh - peers[own])
+__global__ void __launch_bounds__(512) groupnorm_apply_kernel(const __half* __restrict__ x, __half* __restrict__ y,
+                                                              long long img_stride, int HW, int C, int G, int B,
+                                                              const float* __restrict__ fresh, GnPeers peers, int n_peers,
+                                                              int own, int mode, float eps, const __half* __restrict__ gamma,
+                                                              const __half* __restrict__ beta, int silu, int parts) {
+  extern __shared__ float s_ab[];  // [2][C]: scale, shift per channel
+  __shared__ float s_mean[kGnMaxGroups], s_rstd[kGnMaxGroups];
+  const int img = blockIdx.y;
+  const int cpg = C / G;
+  if (threadIdx.x < G) {
+    const int g = threadIdx.x;
+    const long long i1 = (long long)img * G + g, i2 = ((long long)B + img) * G + g;
+    const float f1 = fresh[i1], f2 = fresh[i2];
+    float m1 = f1, m2 = f2;
+    if (mode != 0 && n_peers > 0) {
+      float a1 = 0.f, a2 = 0.f;
+      for (int j = 0; j < n_peers; ++j) {
+        a1 += (mode == 1 && j == own) ? f1 : peers.ptr[j][i1];
+        a2 += (mode == 1 && j == own) ? f2 : peers.ptr[j][i2];
+      }
+      const float inv = 1.f / (float)n_peers;
+      m1 = a1 * inv, m2 = a2 * inv;
+      if (mode == 2) {
+        m1 += f1 - peers.ptr[own][i1];
+        m2 += f2 - peers.ptr[own][i2];
+      }
+    }
+    float var = m2 - m1 * m1;
+    if (var < 0.f) var = f2 - f1 * f1;
+    const float n = (float)((long long)cpg * HW);
+    var *= n / (n - 1.f);
+    s_mean[g] = m1;
+    s_rstd[g] = rsqrtf(var + eps);
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const int g = c / cpg;
+    const float ga = gamma ? __half2float(gamma[c]) : 1.f;
+    const float be = beta ? __half2float(beta[c]) : 0.f;
+    const float a = s_rstd[g] * ga;
+    s_ab[c] = a;
+    s_ab[C + c] = be - s_mean[g] * a;
+  }
+  __syncthreads();
+  const int vecs = C / 8;
+  const int rows = blockDim.x / vecs;
+  const int v = threadIdx.x % vecs, r = threadIdx.x / vecs;
+  if (r >= rows) return;
+  float a[8], b[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) a[j] = s_ab[v * 8 + j], b[j] = s_ab[C + v * 8 + j];
+  const int per = (HW + parts - 1) / parts;
+  const int p0 = blockIdx.x * per, p1 = min(HW, p0 + per);
+  const long long off = (long long)img * img_stride + (long long)v * 8;
+  for (int pix = p0 + r; pix < p1; pix += rows) {
+    const uint4 u = *reinterpret_cast<const uint4*>(x + off + (long long)pix * C);
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+    uint4 o;
+    __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __half22float2(h[j]);
+      float y0 = f.x * a[2 * j] + b[2 * j];
+      float y1 = f.y * a[2 * j + 1] + b[2 * j + 1];
+      if (silu) {
+        y0 = y0 / (1.f + __expf(-y0));
+        y1 = y1 / (1.f + __expf(-y1));
+      }
+      oh[j] = __floats2half2_rn(y0, y1);
+    }
+    *reinterpret_cast<uint4*>(y + off + (long long)pix * C) = o;
+  }
+}
+
+static int gn_threads(int C) {
+  const int vecs = C / 8;
+  int k = 512 / vecs;
+  if (k < 1) k = 1;
+  return vecs * k;
+}
+
+static int gn_parts(int HW, int C, int B) {
+  const int rows = gn_threads(C) / (C / 8);
+  int parts = (HW + rows * 4 - 1) / (rows * 4);  // >= 4 sweeps per CTA
+  const int cap = max(1, (sm_count() * 4) / max(1, B));
+  if (parts > cap) parts = cap;
+  if (parts > kGnMaxParts) parts = kGnMaxParts;
+  if (parts < 1) parts = 1;
+  return parts;
+}
+
+static int gn_check(const char* who, const void* x, int B, int HW, int C, int G, long long img_stride) {
+  if (!x) return fail(kErrInvalidArg, "%s: null input", who);
+  if (B <= 0 || HW <= 0 || C <= 0 || G <= 0) return fail(kErrInvalidArg, "%s: non-positive extent", who);
+  if (C % 8 || C % G) return fail(kErrUnsupported, "%s: C=%d must be a multiple of 8 and of the group count %d", who, C, G);
+  if (C > kGnMaxC || G > kGnMaxGroups || C / 8 > 512) return fail(kErrTooLarge, "%s: C=%d / G=%d beyond the supported maximum", who, C, G);
+  if (img_stride % 8 || (reinterpret_cast<uintptr_t>(x) & 15u)) return fail(kErrInvalidArg, "%s: x must be 16-byte aligned", who);
+  return kOk;
+}
+
+}  // namespace bxl
+
+using namespace bxl;
+
+extern "C" long long bxl_groupnorm_scratch_bytes(int B, int G) {
+  if (B <= 0 || G <= 0) return 0;
+  return 256 + (long long)B * kGnMaxParts * G * 2 * sizeof(float);
+}
+
+extern "C" int bxl_groupnorm_stats_f16(const void* x, long long img_stride, int B, int HW, int C, int G, float* moments,
+                                       void* scratch, long long scratch_bytes, void* stream) {
+  if (int rc = gn_check("bxl_groupnorm_stats_f16", x, B, HW, C, G, img_stride)) return rc;
+  if (!moments || !scratch) return fail(kErrInvalidArg, "bxl_groupnorm_stats_f16: null output/scratch");
+  if (scratch_bytes < bxl_groupnorm_scratch_bytes(B, G)) return fail(kErrTooLarge, "bxl_groupnorm_stats_f16: scratch too small");
+  const int threads = gn_threads(C), parts = gn_parts(HW, C, B);
+  int* ticket = static_cast<int*>(scratch);
+  float* partials = reinterpret_cast<float*>(static_cast<char*>(scratch) + 256);
+  groupnorm_stats_kernel<<<dim3(parts, B), threads, 2 * C * sizeof(float), (cudaStream_t)stream>>>(
+      static_cast<const __half*>(x), img_stride, HW, C, G, parts, partials, ticket, moments, B);
+  return check_cuda(cudaGetLastError(), "groupnorm_stats_kernel launch");
+}
+
+extern "C" int bxl_groupnorm_apply_f16(const void* x, void* y, long long img_stride, int B, int HW, int C, int G,
+                                       const float* fresh_moments, const float* const* peer_moments, int n_peers, int own,
+                                       int mode, float eps, const void* gamma, const void* beta, int silu, void* stream) {
+  if (int rc = gn_check("bxl_groupnorm_apply_f16", x, B, HW, C, G, img_stride)) return rc;
+  if (!y || !fresh_moments) return fail(kErrInvalidArg, "bxl_groupnorm_apply_f16: null pointer");
+  if (mode < 0 || mode > 2) return fail(kErrInvalidArg, "bxl_groupnorm_apply_f16: mode %d", mode);
+  if (mode != 0 && (n_peers < 1 || n_peers > 8 || !peer_moments || own < 0 || own >= n_peers))
+    return fail(kErrInvalidArg, "bxl_groupnorm_apply_f16: bad peer table (n=%d own=%d)", n_peers, own);
+  GnPeers peers;
+  for (int j = 0; j < 8; ++j) peers.ptr[j] = (mode != 0 && j < n_peers) ? peer_moments[j] : nullptr;
+  if (mode != 0)
+    for (int j = 0; j < n_peers; ++j)
+      if (!peers.ptr[j] && !(mode == 1 && j == own)) return fail(kErrInvalidArg, "bxl_groupnorm_apply_f16: peer %d null", j);
+  const int threads = gn_threads(C);
+  const int rows = threads / (C / 8);
+  int parts = (HW + rows * 2 - 1) / (rows * 2);
+  const int cap = max(1, (sm_count() * 8) / B);
+  if (parts > cap) parts = cap;
+  if (parts < 1) parts = 1;
+  groupnorm_apply_kernel<<<dim3(parts, B), threads, 2 * C * sizeof(float), (cudaStream_t)stream>>>(
+      static_cast<const __half*>(x), static_cast<__half*>(y), img_stride, HW, C, G, B, fresh_moments, peers,
+      mode == 0 ? 0 : n_peers, own, mode, eps, static_cast<const __half*>(gamma), static_cast<const __half*>(beta), silu, parts);
+  return check_cuda(cudaGetLastError(), "groupnorm_apply_kernel launch");
+}

@@ -1,0 +1,267 @@
+"""Tensor-level wrappers over the C ABI: torch tensors in, torch tensors out.
+
+PyTorch is used for device memory and streams only; every function here
+launches kernels of libbasedxl_b200 on the current CUDA stream.  Activations
+are NHWC-contiguous ``[B, H, W, C]`` fp16 tensors or ``[..., C]`` matrices.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+_vp = C.c_void_p
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _req(cond: bool, msg: str) -> None:
+    if not cond:
+        raise ValueError(msg)
+
+
+def _f16_cuda(t: torch.Tensor, name: str) -> None:
+    _req(t.is_cuda and t.dtype == torch.float16, f"{name}: expected a CUDA fp16 tensor, got {t.device} {t.dtype}")
+
+
+# --------------------------------------------------------------------------- matmul
+def gemm(a, b, bias=None, residual=None, out=None, b_is_kn=False, out_f32=False):
+    """``a[M,K] @ B`` with ``b`` given as [N,K] (default) or [K,N] (``b_is_kn``)."""
+    _f16_cuda(a, "a"), _f16_cuda(b, "b")
+    _req(a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1, "gemm: 2-D row-major operands")
+    M, K = a.shape
+    N = b.shape[1] if b_is_kn else b.shape[0]
+    _req((b.shape[0] if b_is_kn else b.shape[1]) == K, "gemm: inner dimensions differ")
+    if out is None:
+        out = torch.empty((M, N), device=a.device, dtype=torch.float32 if out_f32 else torch.float16)
+    _req(out.shape == (M, N) and out.stride(1) == 1, "gemm: bad output")
+    if residual is not None:
+        _req(residual.shape == (M, N) and residual.stride(1) == 1, "gemm: bad residual")
+    l = _lib.lib()
+    _lib.check(
+        l.bxl_gemm_f16(
+            _p(a), a.stride(0), _p(b), b.stride(0), int(b_is_kn), _p(bias), _p(residual),
+            0 if residual is None else residual.stride(0), _p(out), out.stride(0), int(out_f32), M, N, K, _stream(),
+        ),
+        l,
+    )
+    return out
+
+
+def linear(x, weight, bias=None, residual=None):
+    """``x[..., K] @ weight[N, K]^T (+ bias) (+ residual[..., N])``."""
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    r2 = None if residual is None else residual.reshape(-1, weight.shape[0])
+    y = gemm(x2, weight, bias=bias, residual=r2)
+    return y.view(*lead, weight.shape[0])
+
+
+def gemm_split_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """fp32 ``a[M,K] @ b[K,N]`` through the split-operand tensor-core product."""
+    _req(a.is_cuda and a.dtype == torch.float32 and b.dtype == torch.float32, "gemm_split_f32: CUDA fp32 operands")
+    a, b = a.contiguous(), b.contiguous()
+    M, K = a.shape
+    N = b.shape[1]
+    l = _lib.lib()
+    ws_bytes = l.bxl_gemm_split_workspace_bytes(M, N, K)
+    ws = torch.empty(ws_bytes, device=a.device, dtype=torch.uint8)
+    out = torch.empty((M, N), device=a.device, dtype=torch.float32)
+    _lib.check(l.bxl_gemm_split_f32(_p(a), _p(b), _p(out), M, N, K, _p(ws), ws_bytes, _stream()), l)
+    return out
+
+
+# --------------------------------------------------------------------------- convolution
+def conv_weight_pack(w_oihw: torch.Tensor) -> torch.Tensor:
+    _f16_cuda(w_oihw, "weight")
+    co, ci, kh, kw = w_oihw.shape
+    _req(kh == 3 and kw == 3, "conv_weight_pack: 3x3 kernels only")
+    w = w_oihw.contiguous()
+    out = torch.empty((co, 9 * ci), device=w.device, dtype=torch.float16)
+    l = _lib.lib()
+    _lib.check(l.bxl_conv_weight_pack_f16(_p(w), _p(out), co, ci, _stream()), l)
+    return out
+
+
+def _halo_args(x, top, bot):
+    B, H, W, Ci = x.shape
+    halo_stride = 0
+    for h in (top, bot):
+        if h is not None:
+            _f16_cuda(h, "halo")
+            _req(h.shape == (B, 1, W, Ci) and h.stride(3) == 1 and h.stride(2) == Ci, "halo rows must be [B,1,W,C]")
+            _req(halo_stride in (0, h.stride(0)), "top and bottom halo must share one image stride")
+            halo_stride = h.stride(0)
+    return halo_stride
+
+
+def _nhwc_strip(x, name):
+    _f16_cuda(x, name)
+    _req(x.dim() == 4, f"{name}: expected [B,H,W,C]")
+    B, H, W, Ci = x.shape
+    _req(x.stride(3) == 1 and x.stride(2) == Ci and x.stride(1) == W * Ci, f"{name}: rows of one image must be NHWC-contiguous")
+
+
+def conv3x3(x, w_packed, bias=None, stride=1, top=None, bot=None, bias_rows=None, residual=None, out=None):
+    """3x3 / pad 1 convolution of an NHWC strip with optional halo rows."""
+    _nhwc_strip(x, "x")
+    B, H, W, Ci = x.shape
+    Co = w_packed.shape[0]
+    _req(w_packed.shape[1] == 9 * Ci, "conv3x3: packed weight does not match C_in")
+    halo_stride = _halo_args(x, top, bot)
+    if out is None:
+        out = torch.empty((B, H // stride, W // stride, Co), device=x.device, dtype=torch.float16)
+    _req(out.is_contiguous(), "conv3x3: output must be contiguous")
+    if residual is not None:
+        _req(residual.shape == out.shape and residual.is_contiguous(), "conv3x3: bad residual")
+    if bias_rows is not None:
+        _req(bias_rows.shape == (B, Co) and bias_rows.is_contiguous(), "conv3x3: bias_rows must be [B,C_out]")
+    l = _lib.lib()
+    if Ci % 64 == 0 and Co % 8 == 0:
+        _lib.check(
+            l.bxl_conv3x3_halo_f16(
+                _p(x), x.stride(0), _p(top), _p(bot), halo_stride, _p(w_packed), _p(bias), _p(bias_rows), _p(residual),
+                _p(out), B, Ci, Co, H, W, stride, _stream(),
+            ),
+            l,
+        )
+    else:
+        _req(stride == 1 and bias_rows is None and residual is None, "conv3x3: thin convolutions are plain stride-1")
+        _lib.check(
+            l.bxl_conv3x3_direct_f16(
+                _p(x), x.stride(0), _p(top), _p(bot), halo_stride, _p(w_packed), _p(bias), _p(out), B, Ci, Co, H, W, _stream()
+            ),
+            l,
+        )
+    return out
+
+
+def halo_pack(x, pad=1, out=None):
+    """``[2, B, pad, W, C]``: the strip's first and last ``pad`` rows."""
+    _nhwc_strip(x, "x")
+    B, H, W, Ci = x.shape
+    if out is None:
+        out = torch.empty((2, B, pad, W, Ci), device=x.device, dtype=torch.float16)
+    _req(out.numel() == 2 * B * pad * W * Ci and out.is_contiguous(), "halo_pack: bad output")
+    l = _lib.lib()
+    _lib.check(l.bxl_halo_pack_f16(_p(x), x.stride(0), _p(out), B, H, W, Ci, pad, _stream()), l)
+    return out
+
+
+# --------------------------------------------------------------------------- GroupNorm
+_gn_scratch: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _scratch(device, nbytes: int) -> torch.Tensor:
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream())
+    t = _gn_scratch.get(key)
+    if t is None or t.numel() < nbytes:
+        t = torch.zeros(max(nbytes, 1 << 20), device=device, dtype=torch.uint8)
+        _gn_scratch[key] = t
+    return t
+
+
+def groupnorm_stats(x, groups: int, out=None):
+    """fp32 moments ``[2, B, G]`` of an NHWC strip (mean, mean of squares per group)."""
+    _nhwc_strip(x, "x")
+    B, H, W, Ci = x.shape
+    if out is None:
+        out = torch.empty((2, B, groups), device=x.device, dtype=torch.float32)
+    _req(out.dtype == torch.float32 and out.numel() == 2 * B * groups and out.is_contiguous(), "groupnorm_stats: bad output")
+    l = _lib.lib()
+    nbytes = l.bxl_groupnorm_scratch_bytes(B, groups)
+    s = _scratch(x.device, nbytes)
+    _lib.check(l.bxl_groupnorm_stats_f16(_p(x), x.stride(0), B, H * W, Ci, groups, _p(out), _p(s), s.numel(), _stream()), l)
+    return out
+
+
+MODE_LOCAL, MODE_SYNC, MODE_STALE = 0, 1, 2
+
+
+def groupnorm_apply(x, groups, eps, gamma, beta, fresh, peers=None, own=0, mode=MODE_LOCAL, silu=False, out=None):
+    _nhwc_strip(x, "x")
+    B, H, W, Ci = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    _req(out.shape == x.shape and out.stride() == x.stride(), "groupnorm_apply: output must match x")
+    n = 0 if peers is None else len(peers)
+    arr = (_vp * max(n, 1))(*[(_p(t) if t is not None else None) for t in (peers or [None])])
+    l = _lib.lib()
+    _lib.check(
+        l.bxl_groupnorm_apply_f16(
+            _p(x), _p(out), x.stride(0), B, H * W, Ci, groups, _p(fresh), arr, n, own, mode, float(eps), _p(gamma), _p(beta),
+            int(silu), _stream(),
+        ),
+        l,
+    )
+    return out
+
+
+# --------------------------------------------------------------------------- attention
+def attention(q, kv_slots, heads: int, scale: float | None = None, out=None):
+    """``q [B, L_q, C]`` against the concatenation of ``kv_slots`` (each
+    ``[B, L_slot, 2C]``: K then V along the last axis).  Head dim 64."""
+    _f16_cuda(q, "q")
+    B, Lq, Cq = q.shape
+    _req(Cq == heads * 64 and q.stride(2) == 1, "attention: head dimension must be 64")
+    s0 = kv_slots[0]
+    Bk, Ls, C2 = s0.shape
+    _req(Bk == B and C2 == 2 * Cq, "attention: slot shape does not match q")
+    for s in kv_slots:
+        _f16_cuda(s, "kv slot")
+        _req(s.shape == s0.shape and s.stride() == s0.stride() and s.stride(2) == 1, "attention: slots must share shape and strides")
+    if out is None:
+        out = torch.empty((B, Lq, Cq), device=q.device, dtype=torch.float16)
+    if scale is None:
+        scale = 64**-0.5
+    arr = (_vp * len(kv_slots))(*[_p(s) for s in kv_slots])
+    l = _lib.lib()
+    _lib.check(
+        l.bxl_attn_fwd_f16(
+            _p(q), q.stride(0), q.stride(1), arr, len(kv_slots), s0.stride(0), s0.stride(1), Cq, _p(out), out.stride(0),
+            out.stride(1), B, heads, Lq, Ls, float(scale), _stream(),
+        ),
+        l,
+    )
+    return out
+
+
+# --------------------------------------------------------------------------- host-graph helpers
+def upsample2x(x):
+    _nhwc_strip(x, "x")
+    _req(x.is_contiguous(), "upsample2x: contiguous input")
+    B, H, W, Ci = x.shape
+    out = torch.empty((B, 2 * H, 2 * W, Ci), device=x.device, dtype=torch.float16)
+    l = _lib.lib()
+    _lib.check(l.bxl_upsample2x_f16(_p(x), _p(out), B, H, W, Ci, _stream()), l)
+    return out
+
+
+def layernorm(x, gamma, beta, eps):
+    _f16_cuda(x, "x")
+    _req(x.is_contiguous(), "layernorm: contiguous input")
+    Ci = x.shape[-1]
+    out = torch.empty_like(x)
+    l = _lib.lib()
+    _lib.check(l.bxl_layernorm_f16(_p(x), _p(out), _p(gamma), _p(beta), x.numel() // Ci, Ci, float(eps), _stream()), l)
+    return out
+
+
+def geglu(h):
+    _f16_cuda(h, "h")
+    _req(h.is_contiguous() and h.shape[-1] % 16 == 0, "geglu: contiguous input with an even number of 8-vectors")
+    F = h.shape[-1] // 2
+    out = torch.empty((*h.shape[:-1], F), device=h.device, dtype=torch.float16)
+    l = _lib.lib()
+    _lib.check(l.bxl_geglu_f16(_p(h), _p(out), h.numel() // (2 * F), F, _stream()), l)
+    return out

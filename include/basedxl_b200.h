@@ -1,0 +1,150 @@
+/* C ABI of libbasedxl_b200: hand-written sm_100a kernels for the displaced
+ * patch-parallel SDXL UNet hot path.
+ *
+ * The reference project (sekstini/basedxl) is pure Python and has no FFI; each
+ * entry point below names the reference code whose device work it replaces
+ * (paths are relative to the reference project).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless stated otherwise; tensors are fp16
+ *     unless the name says f32; activations are NHWC ("channels last") strips or
+ *     [rows, cols] matrices; all strides / leading dimensions are in ELEMENTS
+ *   - `stream` is a cudaStream_t passed as void*; calls only enqueue work
+ *   - no entry point allocates or frees device memory, none synchronises the
+ *     host except bxl_device_status(); workspaces are caller-owned
+ *   - return value: 0 = ok, negative = error (see bxl_last_error()); exceptions
+ *     never cross this boundary
+ *   - one host thread per process drives the library
+ */
+#ifndef BASEDXL_B200_H
+#define BASEDXL_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- library ------------------------------------------------------------ */
+
+/* Sets up the per-device status word and the TMA descriptor encoder for the
+ * current device; fails on anything but compute capability 10.x.
+ * Replaces: device selection in BasedXLConfig.__post_init__ (basedxl/utils.py:22-33),
+ * without its silent fallback to single-device mode. */
+int bxl_init(void);
+
+/* Message of the last failed call on this host thread. */
+const char* bxl_last_error(void);
+
+/* Reads (and clears) the device status word that kernels write when a bounded
+ * wait gives up.  Blocks the host on a small device->host copy. */
+int bxl_device_status(int* code, int* site, int* block);
+
+int bxl_sm_count(void);
+
+/* ---- matmul ------------------------------------------------------------- */
+
+/* C[M,N] = A[M,K] * B (+ bias[N]) (+ residual[M,N]); fp16 operands, fp32
+ * accumulation in tensor memory, output fp16 (out_f32 = 0) or fp32.
+ * b_is_kn = 0: B is [N,K] (an nn.Linear weight as stored).
+ * b_is_kn = 1: B is [K,N] row-major (the layout BasedXLLowPLinear keeps).
+ * Replaces: cascaded_lowp_matmul / _matmul_kernel
+ * (basedxl/triton/cascaded_lowp_matmul.py:54-173), the bias add of
+ * BasedXLLowPLinear.forward (basedxl/modules/lowp_linear.py:15-19) and the
+ * to_q / to_kv / to_out linears of the attention wrappers
+ * (basedxl/modules/attn.py:123,127,159). */
+int bxl_gemm_f16(const void* A, long long lda, const void* B, long long ldb, int b_is_kn, const void* bias,
+                 const void* residual, long long ldr, void* C, long long ldc, int out_f32, int M, int N, int K,
+                 void* stream);
+
+/* Split-operand product of fp32 matrices: A[M,K] and B[K,N] (row-major fp32) are
+ * each split into fp16 high and low parts and C = Ah*Bh + Ah*Bl + Al*Bh is
+ * accumulated in one fp32 tensor-memory accumulator; C is fp32 [M,N].
+ * Replaces: the same reference kernel as bxl_gemm_f16, for fp32 operands (the
+ * reference's accuracy study, extras/measure_cascaded_lowp_matmul_error.py:12-41). */
+long long bxl_gemm_split_workspace_bytes(int M, int N, int K);
+int bxl_gemm_split_f32(const float* A, const float* B, float* C, int M, int N, int K, void* workspace,
+                       long long workspace_bytes, void* stream);
+
+/* ---- convolution ---------------------------------------------------------- */
+
+/* [C_out][C_in][3][3] -> [C_out][ky][kx][C_in], the weight layout both
+ * convolution entry points consume.  Done once per layer at wrap time, like the
+ * reference's fused/transposed weight copies (basedxl/modules/lowp_linear.py:12). */
+int bxl_conv_weight_pack_f16(const void* w_oihw, void* w_packed, int c_out, int c_in, void* stream);
+
+/* 3x3 convolution, padding 1, stride 1 or 2, of an NHWC H-strip x[B,H_in,W,C_in]
+ * whose missing rows above / below come from `top` / `bot` ([B,1,W,C_in], image
+ * stride halo_img_stride; NULL = zero row, i.e. the image edge).  Output
+ * y[B,H_in/stride,W/stride,C_out] (+ bias[C_out]) (+ bias_rows[B,C_out])
+ * (+ residual, same shape as y).  Implicit GEMM on tcgen05; C_in % 64 == 0.
+ * Replaces: BasedConv2dPP.forward's padded-input assembly and F.conv2d
+ * (basedxl/modules/conv2d.py:74-104) and naive_forward (:15-18). */
+int bxl_conv3x3_halo_f16(const void* x, long long x_img_stride, const void* top, const void* bot,
+                         long long halo_img_stride, const void* w_packed, const void* bias, const void* bias_rows,
+                         const void* residual, void* y, int B, int C_in, int C_out, int H_in, int W, int stride,
+                         void* stream);
+
+/* Same contract, stride 1, for the two thin convolutions at the ends of the
+ * network (C_in <= 16, or C_out == 4): direct CUDA-core kernels.
+ * Replaces: BasedConv2dPP.sliced_forward (basedxl/modules/conv2d.py:20-41) for
+ * conv_in, and the forward above for conv_out. */
+int bxl_conv3x3_direct_f16(const void* x, long long x_img_stride, const void* top, const void* bot,
+                           long long halo_img_stride, const void* w_packed, const void* bias, void* y, int B, int C_in,
+                           int C_out, int H, int W, void* stream);
+
+/* First and last `pad` rows of a strip -> out[2][B][pad][W][C].
+ * Replaces: the boundary torch.stack (basedxl/modules/conv2d.py:92) and the copy
+ * into the staging slot in PatchParallelismCommManager.enqueue (basedxl/utils.py:156). */
+int bxl_halo_pack_f16(const void* x, long long img_stride, void* out, int B, int H, int W, int C, int pad, void* stream);
+
+/* ---- GroupNorm -------------------------------------------------------------- */
+
+/* Scratch for bxl_groupnorm_stats_f16.  The first 256 bytes must be zero before
+ * the first use and are left zero by every call; calls sharing a scratch buffer
+ * must be ordered on one stream. */
+long long bxl_groupnorm_scratch_bytes(int B, int G);
+
+/* moments[2][B][G] (fp32): per-group mean and mean of squares of the strip
+ * x[B,HW,C].  Replaces: basedxl/modules/groupnorm.py:38-42. */
+int bxl_groupnorm_stats_f16(const void* x, long long img_stride, int B, int HW, int C, int G, float* moments,
+                            void* scratch, long long scratch_bytes, void* stream);
+
+/* y = GroupNorm(x) (* sigmoid, if silu) using
+ *   mode 0: the strip's own moments                         (groupnorm.py:44-45)
+ *   mode 1: the average of all peers' fresh moments         (groupnorm.py:46-48)
+ *   mode 2: average of stale peer moments + fresh - stale own (groupnorm.py:49-52)
+ * followed by the reference's negative-variance fallback and local-count Bessel
+ * factor (groupnorm.py:56-63) and the affine map (:64-69).
+ * peer_moments: HOST array of n_peers device pointers, each [2][B][G] fp32; in
+ * mode 1 entry `own` is ignored (the fresh moments are used). */
+int bxl_groupnorm_apply_f16(const void* x, void* y, long long img_stride, int B, int HW, int C, int G,
+                            const float* fresh_moments, const float* const* peer_moments, int n_peers, int own, int mode,
+                            float eps, const void* gamma, const void* beta, int silu, void* stream);
+
+/* ---- attention ---------------------------------------------------------------- */
+
+/* out[b, l, h*64 + d] = softmax_l'(q . k * scale) v over the concatenation of
+ * n_slots key/value slots, each [B, L_slot, ld_kv] with K of head h at columns
+ * h*64 and V at v_col0 + h*64.  kv_slots: HOST array of n_slots device pointers
+ * (slot order = token order).  Head dimension 64.
+ * Replaces: the KV concatenation, split, head reshapes and
+ * F.scaled_dot_product_attention of BasedXLSelfAttentionPP._forward
+ * (basedxl/modules/attn.py:129-156) and of BasedXLCrossAttentionPP.forward
+ * (basedxl/modules/attn.py:79-91). */
+int bxl_attn_fwd_f16(const void* q, long long q_img_stride, long long ld_q, const void* const* kv_slots, int n_slots,
+                     long long kv_img_stride, long long ld_kv, int v_col0, void* out, long long out_img_stride,
+                     long long ld_out, int B, int heads, int L_q, int L_slot, float scale, void* stream);
+
+/* ---- host-graph helpers (the elementwise work between the patched operators) -- */
+
+/* y[B,2H,2W,C] = nearest-neighbour up-sampling of x[B,H,W,C]. */
+int bxl_upsample2x_f16(const void* x, void* y, int B, int H, int W, int C, void* stream);
+/* LayerNorm over the last axis of x[rows,C]. */
+int bxl_layernorm_f16(const void* x, void* y, const void* gamma, const void* beta, long long rows, int C, float eps,
+                      void* stream);
+/* out[rows,F] = h[:, :F] * gelu(h[:, F:]) for h[rows,2F] (exact erf GELU). */
+int bxl_geglu_f16(const void* h, void* out, long long rows, int F, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BASEDXL_B200_H */

@@ -1,0 +1,109 @@
+"""tcgen05 GEMM through the C ABI against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import matmul as om
+from tests._util import assert_close, cuda_or_skip, h16
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from basedxl_b200 import _lib, ops
+
+    return _lib, ops
+
+
+@pytest.mark.parametrize(
+    "M,K,N",
+    [
+        (128, 64, 128),      # one tile, one k-block
+        (128, 256, 256),     # 256-wide tile
+        (256, 320, 320),     # N not a tile multiple, K = 5 blocks
+        (300, 200, 136),     # ragged M, K tail (200 = 3*64 + 8), ragged N
+        (2, 320, 1280),      # the time-embedding linear
+        (154, 2048, 640),    # cross-attention K/V projection of 2 x 77 tokens
+        (1024, 2048, 1024),  # the reference unit test's kernel-reaching shape
+        (8192, 640, 640),
+        (2048, 1280, 10240),
+    ],
+)
+@pytest.mark.parametrize("b_is_kn", [False, True])
+def test_gemm_matches_oracle(M, K, N, b_is_kn):
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    g = torch.Generator().manual_seed(M * 7 + K * 3 + N)
+    a = torch.randn(M, K, generator=g)
+    w = torch.randn(N, K, generator=g) / K**0.5
+    bias = torch.randn(N, generator=g)
+    ref = h16(a) @ h16(w).t() + h16(bias)
+    b_dev = (w.t().contiguous() if b_is_kn else w).half().to(dev)
+    y = ops.gemm(a.half().to(dev), b_dev, bias=bias.half().to(dev), b_is_kn=b_is_kn)
+    _lib.device_status()
+    assert_close(y, ref, what=f"gemm {M}x{K}x{N} kn={b_is_kn}")
+
+
+def test_gemm_residual_and_strided_output():
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    g = torch.Generator().manual_seed(5)
+    M, K, N = 384, 640, 1280
+    a, w, r = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g) / K**0.5, torch.randn(M, N, generator=g)
+    ref = h16(a) @ h16(w).t() + h16(r)
+    big = torch.zeros(M, 2 * N, device=dev, dtype=torch.float16)
+    out = big[:, N:]  # row stride 2N: the K/V slot case
+    ops.gemm(a.half().to(dev), w.half().to(dev), residual=r.half().to(dev), out=out)
+    _lib.device_status()
+    assert_close(out, ref, what="gemm residual/strided")
+    assert float(big[:, :N].abs().max()) == 0.0
+
+
+def test_gemm_reference_unit_test_tolerance():
+    # tests/test_cascaded_lowp_matmul.py:26 of the reference: rtol 1e-3, atol 0.35 vs torch.matmul
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    g = torch.Generator().manual_seed(11)
+    a, b = torch.randn(1024, 2048, generator=g).half(), torch.randn(2048, 1024, generator=g).half()
+    y = ops.gemm(a.to(dev), b.to(dev), b_is_kn=True)
+    _lib.device_status()
+    expected = (a.float() @ b.float()).half()
+    assert torch.allclose(y.cpu(), expected, rtol=1e-3, atol=0.35)
+
+
+@pytest.mark.parametrize("M,K,N", [(8192, 640, 640), (2048, 1280, 1280), (16384, 320, 320)])
+def test_error_vs_fp64_no_worse_than_reference_kernel(M, K, N):
+    """Method of the reference's error study: fp64 product as truth."""
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    torch.manual_seed(0)
+    a32, b32 = torch.randn(M, K), torch.randn(K, N)
+    a16, b16 = a32.half(), b32.half()
+    # (i) fp16 operands: new kernel vs the optimistic model of the reference kernel
+    exp16 = om.matmul_fp64(a16, b16)
+    y16 = ops.gemm(a16.to(dev), b16.to(dev), b_is_kn=True).cpu()
+    _lib.device_status()
+    e_new = om.error_table(exp16, y16)
+    sub = slice(0, 512)  # the model is slow: bound it on a row block
+    e_ref = om.error_table(exp16[sub], om.matmul_fp16_accumulate(a16[sub], b16, block_k=32, model="block"))
+    e_new_sub = om.error_table(exp16[sub], y16[sub])
+    assert e_new_sub["l1"] <= e_ref["l1"] and e_new_sub["mse"] <= e_ref["mse"]
+    assert e_new_sub["rel_median"] <= e_ref["rel_median"]
+    # (ii) fp32 operands through the split-operand product: far below fp16-operand rounding
+    exp32 = om.matmul_fp64(a32, b32)
+    y32 = ops.gemm_split_f32(a32.to(dev), b32.to(dev)).cpu()
+    _lib.device_status()
+    e_split = om.error_table(exp32, y32)
+    e_half = om.error_table(exp32, y16)
+    assert e_split["max"] < 1e-3 * max(1.0, K**0.5)
+    assert e_split["l1"] < 0.05 * e_half["l1"]  # tensor-core fp32 accumulation truncates; still ~50x below fp16 operands
+    assert e_new["max"] < 0.35
+
+
+def test_bad_arguments_are_rejected():
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    a = torch.zeros(128, 68, device=dev, dtype=torch.float16)  # K = 68: row stride not 16-byte granular
+    w = torch.zeros(128, 68, device=dev, dtype=torch.float16)
+    with pytest.raises(_lib.BxlError):
+        ops.gemm(a, w)
