@@ -74,19 +74,26 @@ def lib() -> C.CDLL:
     dev = torch.cuda.current_device()
     if dev not in _inited_devices:
         torch.cuda.init()
-        check(l.bxl_init(), l)
+        check(l.bxl_init(), l, kernels=0)
         _inited_devices.add(dev)
     return l
 
 
-def check(rc: int, l: C.CDLL | None = None) -> None:
+# kernels of this library enqueued so far by this process (each successful
+# compute call adds the number of kernels it launches)
+launches = 0
+
+
+def check(rc: int, l: C.CDLL | None = None, kernels: int = 1) -> None:
+    global launches
     if rc != 0:
         l = l or load()
         raise BxlError(f"libbasedxl_b200 error {rc}: {l.bxl_last_error().decode()}")
+    launches += kernels
 
 
 def device_status() -> None:
     """Synchronise and raise if any kernel recorded a failed bounded wait."""
     l = lib()
     code, site, block = _i(0), _i(0), _i(0)
-    check(l.bxl_device_status(C.byref(code), C.byref(site), C.byref(block)), l)
+    check(l.bxl_device_status(C.byref(code), C.byref(site), C.byref(block)), l, kernels=0)

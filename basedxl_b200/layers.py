@@ -1,0 +1,124 @@
+"""Leaf layers of the host UNet graph, backed by the library's kernels.
+
+Each class subclasses the ``torch.nn`` module it stands for, so parameter
+names, ``state_dict`` layout and ``isinstance`` checks (the patch-parallel swap
+in ``basedxl_b200.unet`` keys on ``nn.Conv2d`` / ``nn.GroupNorm`` / ``Attention``)
+are the stock ones; only ``forward`` differs: it launches sm_100a kernels and
+has no other path.
+
+Image tensors are ``[B, C, H, W]``-shaped with channels-last strides.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from . import ops
+from .modules.attn import _finish, _lin, fuse_kv
+from .modules.base_module import as_nchw, as_nhwc
+from .modules.conv2d import check_conv, packed_weight
+
+
+class Conv2d(nn.Conv2d):
+    supports_fused_epilogue = True
+
+    def forward(self, x, *args, bias_rows=None, residual=None, **kwargs):
+        if tuple(self.kernel_size) == (1, 1):
+            # 1x1 convolution = a matmul over NHWC pixels
+            xh = as_nhwc(x)
+            b, h, w, c = xh.shape
+            r2 = None if residual is None else as_nhwc(residual).reshape(-1, self.out_channels)
+            y = ops.gemm(xh.reshape(-1, c), self.weight.view(self.out_channels, c), bias=self.bias, residual=r2)
+            return as_nchw(y.view(b, h, w, self.out_channels))
+        check_conv(self)
+        fused = {}
+        if bias_rows is not None:
+            fused["bias_rows"] = bias_rows
+        if residual is not None:
+            fused["residual"] = as_nhwc(residual)
+        y = ops.conv3x3(as_nhwc(x), packed_weight(self), self.bias, stride=self.stride[0], **fused)
+        return as_nchw(y)
+
+
+class GroupNorm(nn.GroupNorm):
+    supports_fused_epilogue = True
+    fuse_silu = False  # set per instance by the host graph where a SiLU follows
+
+    def forward(self, x, silu=None):
+        if silu is None:
+            silu = self.fuse_silu
+        xh = as_nhwc(x)
+        fresh = ops.groupnorm_stats(xh, self.num_groups)
+        y = ops.groupnorm_apply(
+            xh, self.num_groups, self.eps, self.weight if self.affine else None, self.bias if self.affine else None,
+            fresh, None, 0, ops.MODE_LOCAL, silu=silu,
+        )
+        return as_nchw(y)
+
+
+class Linear(nn.Linear):
+    supports_fused_epilogue = True
+
+    def forward(self, x, residual=None):
+        return _lin(self, x, residual=residual)
+
+
+class LayerNorm(nn.LayerNorm):
+    def forward(self, x):
+        return ops.layernorm(x if x.is_contiguous() else x.contiguous(), self.weight, self.bias, self.eps)
+
+
+class Attention(nn.Module):
+    """Multi-head attention block with the attribute surface the patch-parallel
+    wrappers read: ``to_q, to_k, to_v, to_out[0], to_out[1], heads,
+    residual_connection, rescale_output_factor``.  Head dimension 64."""
+
+    supports_fused_epilogue = True
+
+    def __init__(self, query_dim: int, heads: int, cross_attention_dim: int | None = None, linear_cls=Linear):
+        super().__init__()
+        ctx = cross_attention_dim or query_dim
+        self.heads = heads
+        self.is_cross = cross_attention_dim is not None
+        self.to_q = linear_cls(query_dim, query_dim, bias=False)
+        self.to_k = linear_cls(ctx, query_dim, bias=False)
+        self.to_v = linear_cls(ctx, query_dim, bias=False)
+        self.to_out = nn.ModuleList([linear_cls(query_dim, query_dim, bias=True), nn.Dropout(0.0)])
+        self.residual_connection = False
+        self.rescale_output_factor = 1.0
+        self._kv = None
+
+    def _fused_kv(self) -> nn.Linear:
+        key = (self.to_k.weight.data_ptr(), self.to_k.weight._version, self.to_v.weight._version)
+        if self._kv is None or self._kv[0] != key:
+            self._kv = (key, fuse_kv(self.to_k, self.to_v))
+        return self._kv[1]
+
+    def forward(self, hidden_states, encoder_hidden_states=None, scale: float = 1.0, *args, residual=None, **kwargs):
+        ctx = hidden_states if encoder_hidden_states is None else encoder_hidden_states
+        q = _lin(self.to_q, hidden_states)
+        kv = _lin(self._fused_kv(), ctx)
+        o = ops.attention(q, [kv], self.heads)
+        return _finish(self, o, hidden_states, residual)
+
+
+def silu(x):
+    return torch.nn.functional.silu(x)
+
+
+def geglu(h):
+    return ops.geglu(h if h.is_contiguous() else h.contiguous())
+
+
+def upsample2x(x):
+    return as_nchw(ops.upsample2x(as_nhwc(x)))
+
+
+class KernelLayers:
+    """Layer factory handed to the host graph: everything runs on the library."""
+
+    Conv2d, GroupNorm, Linear, LayerNorm, Attention = Conv2d, GroupNorm, Linear, LayerNorm, Attention
+    silu = staticmethod(silu)
+    geglu = staticmethod(geglu)
+    upsample2x = staticmethod(upsample2x)
+    memory_format = torch.channels_last

@@ -1,0 +1,134 @@
+"""Patch-parallel attention wrappers (reference: basedxl/modules/attn.py).
+
+``BasedXLSelfAttentionPP``: local queries against the full key/value sequence,
+which lives as one ``[B, L_local, 2C]`` slot per strip inside the comm
+manager's staging buffers.  The fused ``to_kv`` projection writes this strip's
+fresh K/V straight into its own slot, and the attention kernel reads all slots
+in place (no concatenation).
+
+``BasedXLCrossAttentionPP``: K/V of the text context are computed once per
+image (``counter == 0``) and cached.
+
+The wrapped module must expose what the reference reads off diffusers'
+``Attention``: ``to_q, to_k, to_v, to_out[0], to_out[1], heads,
+residual_connection, rescale_output_factor`` (attn.py:16-17,69,82,94-101).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+from torch import distributed as dist
+
+from .. import ops
+from ..utils import BasedXLConfig
+from .base_module import BaseModule
+
+
+def fuse_kv(to_k: nn.Linear, to_v: nn.Linear) -> nn.Linear:
+    """One Linear with weight [W_k; W_v] (basedxl/modules/attn.py:16-39)."""
+    assert isinstance(to_k, nn.Linear) and isinstance(to_v, nn.Linear)
+    assert (to_k.bias is None) == (to_v.bias is None)
+    assert to_k.weight.shape == to_v.weight.shape
+    in_size, out_size = to_k.in_features, to_k.out_features
+    to_kv = nn.Linear(in_size, out_size * 2, bias=to_k.bias is not None, device=to_k.weight.device, dtype=to_k.weight.dtype)
+    to_kv.weight.data[:out_size].copy_(to_k.weight.data)
+    to_kv.weight.data[out_size:].copy_(to_v.weight.data)
+    if to_k.bias is not None:
+        to_kv.bias.data[:out_size].copy_(to_k.bias.data)
+        to_kv.bias.data[out_size:].copy_(to_v.bias.data)
+    return to_kv
+
+
+def _lin(layer: nn.Linear, x: torch.Tensor, residual=None, out=None) -> torch.Tensor:
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    r2 = None if residual is None else residual.reshape(-1, layer.out_features)
+    y = ops.gemm(x2, layer.weight, bias=layer.bias, residual=r2, out=out)
+    return y.view(*lead, layer.out_features)
+
+
+def _finish(attn, o: torch.Tensor, hidden_in: torch.Tensor, residual) -> torch.Tensor:
+    """to_out projection (+ fused residual), then the module's own residual /
+    rescale options (basedxl/modules/attn.py:158-166)."""
+    y = _lin(attn.to_out[0], o, residual=residual)
+    # to_out[1] is a Dropout; inference only
+    if attn.residual_connection:
+        y = y + hidden_in
+    if attn.rescale_output_factor != 1.0:
+        y = y / attn.rescale_output_factor
+    return y
+
+
+class BasedXLAttentionPP(BaseModule):
+    def __init__(self, module: nn.Module, basedxl_config: BasedXLConfig):
+        super().__init__(module, basedxl_config)
+        self.to_kv = fuse_kv(module.to_k, module.to_v)
+
+
+class BasedXLCrossAttentionPP(BasedXLAttentionPP):
+    def __init__(self, module: nn.Module, basedxl_config: BasedXLConfig):
+        super().__init__(module, basedxl_config)
+        self.kv_cache = None
+
+    def forward(self, hidden_states, encoder_hidden_states=None, scale: float = 1.0, *args, residual=None, **kwargs):
+        torch.cuda.nvtx.range_push("cross_attn::forward")
+        assert encoder_hidden_states is not None
+        attn = self.module
+        recompute_kv = self.counter == 0
+        q = _lin(attn.to_q, hidden_states)
+        if recompute_kv or self.kv_cache is None:
+            self.kv_cache = _lin(self.to_kv, encoder_hidden_states)
+        o = ops.attention(q, [self.kv_cache], attn.heads)
+        y = _finish(attn, o, hidden_states, residual)
+        self.counter += 1
+        torch.cuda.nvtx.range_pop()
+        return y
+
+
+class BasedXLSelfAttentionPP(BasedXLAttentionPP):
+    def __init__(self, module: nn.Module, basedxl_config: BasedXLConfig):
+        super().__init__(module, basedxl_config)
+
+    def _forward(self, hidden_states: torch.Tensor, scale: float = 1.0, residual=None):
+        attn = self.module
+        cfg = self.basedxl_config
+        assert self.comm_manager is not None
+        n, idx = cfg.n_device_per_batch, cfg.split_idx()
+        b, l, c = hidden_states.shape
+        q = _lin(attn.to_q, hidden_states)
+        if n == 1:
+            slots = [_lin(self.to_kv, hidden_states)]
+        elif self.buffer_list is None:
+            # no staging buffers yet: own K/V stands in for every strip (attn.py:132-133)
+            kv = _lin(self.to_kv, hidden_states)
+            slots = [kv] * n
+        elif self.counter <= cfg.warmup_steps:
+            kv = _lin(self.to_kv, hidden_states)
+            dist.all_gather(self.buffer_list, kv, group=cfg.batch_group, async_op=False)
+            slots = list(self.buffer_list)
+        else:
+            # fresh K/V is produced directly in the own staging slot; peers' slots are
+            # one step stale (attn.py:138-141)
+            own = self.buffer_list[idx]
+            _lin(self.to_kv, hidden_states, out=own.view(b * l, -1))
+            slots = list(self.buffer_list)
+            self.comm_manager.enqueue(self.idx, own)
+        o = ops.attention(q, slots, attn.heads)
+        return _finish(attn, o, hidden_states, residual)
+
+    def forward(self, hidden_states, encoder_hidden_states=None, scale: float = 1.0, *args, residual=None, **kwargs):
+        torch.cuda.nvtx.range_push("self_attn::forward")
+        cfg = self.basedxl_config
+        self._wait_pending()
+        b, l, c = hidden_states.shape
+        if cfg.n_device_per_batch > 1 and self.buffer_list is None and self.comm_manager is not None:
+            if self.comm_manager.buffer_list is None:
+                self.idx = self.comm_manager.register_tensor(
+                    shape=(b, l, self.to_kv.out_features), torch_dtype=hidden_states.dtype, layer_type="attn"
+                )
+            else:
+                self.buffer_list = self.comm_manager.get_buffer_list(self.idx)
+        output = self._forward(hidden_states, scale=scale, residual=residual)
+        self.counter += 1
+        torch.cuda.nvtx.range_pop()
+        return output

@@ -1,0 +1,60 @@
+"""Patch-parallel GroupNorm (reference: basedxl/modules/groupnorm.py:9-72),
+optionally fused with the SiLU that follows it in the host graph (the wrapped
+module carries ``fuse_silu = True`` in that case).
+
+Moments are kept in fp32.  The reference registers ``[2, B, G, 1, 1, 1]`` values
+in the activation dtype per layer; here each fp32 moment occupies two fp16
+slots of the shared staging buffer, i.e. the registered shape is
+``[2, B, G, 1, 1, 2]``.
+"""
+from __future__ import annotations
+
+import torch
+from torch import distributed as dist
+from torch import nn
+
+from .. import ops
+from ..utils import BasedXLConfig
+from .base_module import BaseModule, as_nchw, as_nhwc
+
+
+class BasedXLGroupNorm(BaseModule):
+    def __init__(self, module: nn.GroupNorm, basedxl_config: BasedXLConfig):
+        assert isinstance(module, nn.GroupNorm)
+        super().__init__(module, basedxl_config)
+
+    def forward(self, x: torch.Tensor, silu: bool | None = None) -> torch.Tensor:
+        torch.cuda.nvtx.range_push("group_norm::forward")
+        m = self.module
+        cfg = self.basedxl_config
+        self._wait_pending()
+        assert x.ndim == 4
+        n, c, h, w = x.shape
+        groups = m.num_groups
+        if silu is None:
+            silu = bool(getattr(m, "fuse_silu", False))
+
+        if self.buffer_list is None and self.comm_manager is not None:
+            if self.comm_manager.buffer_list is None:
+                self.idx = self.comm_manager.register_tensor(
+                    shape=[2, n, groups, 1, 1, 2], torch_dtype=x.dtype, layer_type="gn"
+                )
+            else:
+                self.buffer_list = [t.view(-1).view(torch.float32) for t in self.comm_manager.get_buffer_list(self.idx)]
+
+        xh = as_nhwc(x)
+        fresh = ops.groupnorm_stats(xh, groups)  # [2, B, G] fp32
+        gamma = m.weight if m.affine else None
+        beta = m.bias if m.affine else None
+        if self.buffer_list is None:
+            y = ops.groupnorm_apply(xh, groups, m.eps, gamma, beta, fresh, None, 0, ops.MODE_LOCAL, silu=silu)
+        elif self.counter <= cfg.warmup_steps:
+            dist.all_gather(self.buffer_list, fresh.view(-1), group=cfg.batch_group, async_op=False)
+            y = ops.groupnorm_apply(xh, groups, m.eps, gamma, beta, fresh, self.buffer_list, cfg.split_idx(), ops.MODE_SYNC, silu=silu)
+        else:
+            y = ops.groupnorm_apply(xh, groups, m.eps, gamma, beta, fresh, self.buffer_list, cfg.split_idx(), ops.MODE_STALE, silu=silu)
+            assert self.comm_manager is not None
+            self.comm_manager.enqueue(self.idx, fresh.view(-1))
+        self.counter += 1
+        torch.cuda.nvtx.range_pop()
+        return as_nchw(y)

@@ -77,7 +77,7 @@ def gemm_split_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     ws_bytes = l.bxl_gemm_split_workspace_bytes(M, N, K)
     ws = torch.empty(ws_bytes, device=a.device, dtype=torch.uint8)
     out = torch.empty((M, N), device=a.device, dtype=torch.float32)
-    _lib.check(l.bxl_gemm_split_f32(_p(a), _p(b), _p(out), M, N, K, _p(ws), ws_bytes, _stream()), l)
+    _lib.check(l.bxl_gemm_split_f32(_p(a), _p(b), _p(out), M, N, K, _p(ws), ws_bytes, _stream()), l, kernels=3)
     return out
 
 

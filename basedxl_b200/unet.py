@@ -1,0 +1,182 @@
+"""UNet wrapper: patched-module swap, CFG / strip dispatch, output gather
+(reference: basedxl/unet.py:18-199).
+
+``BasedXLUnet(model, cfg)`` takes a host UNet graph (``basedxl_b200.sdxl_unet``
+or anything with the same child-module naming) and, when patch parallelism is
+on, replaces in place every non-1x1 ``nn.Conv2d``, every ``nn.GroupNorm`` and
+every attention child named ``attn1`` / ``attn2`` by its patch-parallel wrapper
+(basedxl/unet.py:89-114); with ``fp16_acc_matmul`` every ``nn.Linear`` is
+replaced by ``BasedXLLowPLinear`` (:81-87).
+
+The reference never constructs its comm manager (nothing calls
+``set_comm_manager`` / ``create_buffer``); ``prepare`` below supplies that
+sequence and ``forward`` calls it on first use.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .modules.attn import BasedXLCrossAttentionPP, BasedXLSelfAttentionPP
+from .modules.base_module import BaseModule
+from .modules.conv2d import BasedConv2dPP
+from .modules.groupnorm import BasedXLGroupNorm
+from .modules.lowp_linear import BasedXLLowPLinear
+from .utils import BasedXLConfig, PatchParallelismCommManager
+
+
+def _is_attention(m: nn.Module) -> bool:
+    return all(hasattr(m, a) for a in ("to_q", "to_k", "to_v", "to_out", "heads"))
+
+
+class BaseModel(nn.Module):
+    def __init__(self, model: nn.Module, basedxl_config: BasedXLConfig):
+        super().__init__()
+        self.model = model
+        self.basedxl_config = basedxl_config
+        self.comm_manager = None
+        self.buffer_list = None
+        self.output_buffer = None
+        self.counter = 0
+
+    def forward(self, *args, **kwargs):
+        raise NotImplementedError
+
+    def set_counter(self, counter: int = 0):
+        self.counter = counter
+        for module in self.model.modules():
+            if isinstance(module, BaseModule):
+                module.set_counter(counter)
+
+    def set_comm_manager(self, comm_manager: PatchParallelismCommManager):
+        self.comm_manager = comm_manager
+        for module in self.model.modules():
+            if isinstance(module, BaseModule):
+                module.set_comm_manager(comm_manager)
+
+    @property
+    def config(self):
+        return self.model.config
+
+    def synchronize(self):
+        if self.comm_manager is not None and self.comm_manager.handles is not None:
+            for i in range(len(self.comm_manager.handles)):
+                if self.comm_manager.handles[i] is not None:
+                    self.comm_manager.handles[i].wait()
+                    self.comm_manager.handles[i] = None
+
+
+class BasedXLUnet(BaseModel):
+    def __init__(self, model: nn.Module, basedxl_config: BasedXLConfig):
+        cfg = basedxl_config
+        self.patched = bool(cfg.patch_parallelism and cfg.world_size > 1 and cfg.n_device_per_batch > 1)
+        if self.patched:
+            self.patch_pp_layers(model, cfg)
+        if cfg.fp16_acc_matmul:
+            self.patch_linear_layers(model)
+        if cfg.compile_unet:
+            raise NotImplementedError(
+                "compile_unet: there is no tracing compiler in this implementation; launch overhead is removed with "
+                "CUDA graphs (BasedXLPipeline(..., cuda_graph=True)) instead"
+            )
+        super().__init__(model, cfg)
+
+    def patch_linear_layers(self, model: nn.Module):
+        for _name, module in model.named_modules():
+            for subname, submodule in module.named_children():
+                if isinstance(submodule, nn.Linear):
+                    setattr(module, subname, BasedXLLowPLinear(submodule))
+
+    def patch_pp_layers(self, model: nn.Module, cfg: BasedXLConfig):
+        for _name, module in model.named_modules():
+            if isinstance(module, BaseModule):
+                continue
+            for subname, submodule in module.named_children():
+                if isinstance(submodule, nn.Conv2d):
+                    ks = submodule.kernel_size
+                    if ks == (1, 1) or ks == 1:
+                        continue
+                    setattr(module, subname, BasedConv2dPP(submodule, cfg, is_first_layer=subname == "conv_in"))
+                elif _is_attention(submodule):
+                    if subname == "attn1":
+                        wrapped = BasedXLSelfAttentionPP(submodule, cfg)
+                    elif subname == "attn2":
+                        wrapped = BasedXLCrossAttentionPP(submodule, cfg)
+                    else:
+                        raise ValueError(f"Unknown attention layer: {subname}")
+                    setattr(module, subname, wrapped)
+                elif isinstance(submodule, nn.GroupNorm):
+                    setattr(module, subname, BasedXLGroupNorm(submodule, cfg))
+
+    def reset(self):
+        """Start a new image: drain the exchange queue and every pending gather,
+        then re-enter the synchronous warm-up phase."""
+        if self.comm_manager is not None:
+            self.comm_manager.clear()
+        self.set_counter(0)
+
+    @property
+    def add_embedding(self):
+        return self.model.add_embedding
+
+    # ------------------------------------------------------------------ set-up
+    @torch.no_grad()
+    def prepare(self, sample, timestep, encoder_hidden_states, added_cond_kwargs=None):
+        """Create the comm manager, let every patched layer register its exchange
+        tensor in one forward pass over its strip, allocate the staging buffers
+        and reset the step counter."""
+        if not self.patched:
+            return
+        cm = PatchParallelismCommManager(self.basedxl_config)
+        self.set_comm_manager(cm)
+        self._run_local(sample, timestep, encoder_hidden_states, added_cond_kwargs or {})
+        cm.create_buffer()
+        self.set_counter(0)
+
+    def _slice_batch(self, sample, timestep, encoder_hidden_states, added_cond_kwargs):
+        cfg = self.basedxl_config
+        if not (cfg.use_cfg and cfg.world_size > 1):
+            return sample, timestep, encoder_hidden_states, added_cond_kwargs
+        assert sample.shape[0] == 2
+        i = cfg.batch_idx()
+        sample = sample[i : i + 1]
+        if isinstance(timestep, torch.Tensor) and timestep.ndim > 0:
+            timestep = timestep[i : i + 1]
+        encoder_hidden_states = encoder_hidden_states[i : i + 1]
+        added_cond_kwargs = {k: v[i : i + 1] for k, v in added_cond_kwargs.items()}
+        return sample, timestep, encoder_hidden_states, added_cond_kwargs
+
+    def _run_local(self, sample, timestep, encoder_hidden_states, added_cond_kwargs):
+        s, t, e, a = self._slice_batch(sample, timestep, encoder_hidden_states, added_cond_kwargs)
+        return self.model(s, t, e, added_cond_kwargs=a, return_dict=False)[0]
+
+    # ------------------------------------------------------------------ one denoising step
+    def forward(self, sample, timestep, encoder_hidden_states, added_cond_kwargs={}, **kwargs):
+        torch.cuda.nvtx.range_push("unet::forward")
+        cfg = self.basedxl_config
+        b, c, h, w = sample.shape
+        if self.patched and self.comm_manager is None:
+            self.prepare(sample, timestep, encoder_hidden_states, added_cond_kwargs)
+
+        if cfg.world_size == 1:
+            output = self.model(sample, timestep, encoder_hidden_states, added_cond_kwargs=added_cond_kwargs, return_dict=False)[0]
+        else:
+            # every rank computes one strip of one CFG half (or of the whole batch)
+            local = self._run_local(sample, timestep, encoder_hidden_states, added_cond_kwargs).contiguous()
+            if self.output_buffer is None:
+                self.output_buffer = torch.empty((b, c, h, w), device=local.device, dtype=local.dtype)
+            if self.buffer_list is None:
+                self.buffer_list = [torch.empty_like(local) for _ in range(cfg.world_size)]
+            dist.all_gather(self.buffer_list, local, async_op=False)
+            n = cfg.n_device_per_batch
+            if cfg.use_cfg:
+                # basedxl/unet.py:172-174: first half of the ranks = batch row 0, second half = row 1
+                torch.cat(self.buffer_list[:n], dim=2, out=self.output_buffer[0:1])
+                torch.cat(self.buffer_list[n:], dim=2, out=self.output_buffer[1:2])
+            else:
+                torch.cat(self.buffer_list, dim=2, out=self.output_buffer)
+            output = self.output_buffer
+        self.counter += 1
+        torch.cuda.nvtx.range_pop()
+        return (output,)

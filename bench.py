@@ -1,0 +1,355 @@
+"""Benchmark of the SDXL 1024^2 UNet denoising loop.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One JSON line on stdout (rank 0).  A *step* is one denoising step of the loop:
+UNet forward on the CFG batch of 2 (split over the ranks as the reference's
+config does: CFG halves first, then H-strips), guidance combine, Euler update.
+``value`` is seconds per 50-step image = 50 x the mean step time, with every
+input resident in device memory; a timed region of K = 50 steps started from a
+fresh image contains the reference's 5 synchronous warm-up steps followed by 45
+displaced steps, like a real image.  ``e2e`` is the same figure measured through
+``BasedXLPipeline.__call__`` with pinned HOST conditioning / latents in and the
+final latent copied back out inside the timed region.
+
+``--impl reference`` times the reference's CPU path instead: the same UNet graph
+evaluated by stock PyTorch fp32 operators on the host cores (the reference has no
+CPU implementation other than its PyTorch modules on CPU tensors), on a bounded
+sample per step, extrapolated to s/image by algorithmic FLOPs.
+
+Synthetic data throughout: N(0,1) latents and conditioning, seed-0 random
+weights of the SDXL architecture.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+IMAGE_STEPS = 50
+METRIC = "sdxl_1024_50step_unet_s_per_image"
+UNIT = "s/image"
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"tflops_burst": p["bf16_tflops"], "tflops_sustained": p["bf16_tflops_sustained"], "hbm_gbs": p["hbm_gbs"], "source": "measured"}
+    return {"tflops_burst": 1590.0, "tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "power_w_max": max(power), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- synthetic inputs
+def synthetic_inputs(height, width, pin: bool):
+    g = torch.Generator().manual_seed(1234)
+    t = {
+        "latents": torch.randn(1, 4, height // 8, width // 8, generator=g),
+        "prompt_embeds": torch.randn(1, 77, 2048, generator=g),
+        "negative_prompt_embeds": torch.randn(1, 77, 2048, generator=g),
+        "pooled_prompt_embeds": torch.randn(1, 1280, generator=g),
+        "negative_pooled_prompt_embeds": torch.randn(1, 1280, generator=g),
+    }
+    if pin:
+        t = {k: v.pin_memory() for k, v in t.items()}
+    return t
+
+
+# --------------------------------------------------------------------------- GEMM kernel roofline
+def gemm_kernel_roofline(device, n_strips: int, height: int, width: int, peaks) -> dict:
+    """The dominant kernel (the tcgen05 GEMM: 64 % of the loop's FLOPs at 1024^2)
+    timed launch by launch with CUDA events on the launching stream, over the
+    UNet's own linear-layer shapes, L2 flushed between launches.  ``achieved`` =
+    sum of algorithmic FLOPs (2*M*N*K) / sum of launch durations."""
+    from basedxl_b200 import ops
+
+    hw = (height // 8) * (width // 8) // n_strips
+    # (tokens, K, N, launches per UNet forward) of the per-rank (b = 1 at N > 1, b = 2 at N = 1) linears
+    b = 2 if n_strips == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1 else 1
+    shapes = [
+        (b * hw // 4, 640, 640, 50), (b * hw // 4, 640, 1280, 10), (b * hw // 4, 640, 5120, 10), (b * hw // 4, 2560, 640, 10),
+        (b * hw // 16, 1280, 1280, 252), (b * hw // 16, 1280, 2560, 60), (b * hw // 16, 1280, 10240, 60), (b * hw // 16, 5120, 1280, 60),
+    ]
+    flush = torch.empty(256 << 20, device=device, dtype=torch.uint8)
+    stream = torch.cuda.current_stream()
+    tot_flops = tot_ms = 0.0
+    per_shape = []
+    for (M, K, N, count) in shapes:
+        a = torch.randn(M, K, device=device).half()
+        w = torch.randn(N, K, device=device).half()
+        out = torch.empty(M, N, device=device, dtype=torch.float16)
+        for _ in range(3):
+            ops.gemm(a, w, out=out)
+        times = []
+        for _ in range(5):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            ops.gemm(a, w, out=out)
+            e1.record(stream)
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1))
+        ms = statistics.median(times)
+        fl = 2.0 * M * N * K
+        per_shape.append({"M": M, "K": K, "N": N, "launches_per_forward": count, "us": round(ms * 1e3, 2), "tflops": round(fl / ms / 1e9, 1)})
+        tot_flops += fl * count
+        tot_ms += ms * count
+    achieved = tot_flops / tot_ms / 1e9
+    return {
+        "bound": "tensor", "kernel": "gemm_conv_kernel (linear layers)", "achieved": round(achieved, 1),
+        "peak": peaks["tflops_burst"], "peak_kind": f"{peaks['source']} burst (kernel timed alone)", "unit": "TFLOP/s",
+        "frac": round(achieved / peaks["tflops_burst"], 4), "traffic": None, "per_shape": per_shape,
+    }
+
+
+# --------------------------------------------------------------------------- CPU baseline (oracle port)
+def cpu_unet(state_dict=None):
+    from basedxl_b200.sdxl_unet import UNet2DConditionModel, sdxl_config
+    from oracle.torch_layers import TorchLayers
+
+    torch.manual_seed(0)
+    with torch.device("meta"):
+        m = UNet2DConditionModel(sdxl_config(), layers=TorchLayers)
+    m = m.to_empty(device="cpu").eval()
+    if state_dict is not None:
+        m.load_state_dict({k: v.float().cpu() for k, v in state_dict.items()})
+    else:
+        with torch.no_grad():
+            for p in m.parameters():
+                p.uniform_(-0.02, 0.02)
+    return m
+
+
+def cpu_forward_seconds(model, latent_hw: int, batch: int = 2) -> float:
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(batch, 4, latent_hw, latent_hw, generator=g)
+    ehs = torch.randn(batch, 77, 2048, generator=g)
+    added = {"text_embeds": torch.randn(batch, 1280, generator=g), "time_ids": torch.tensor([[1024.0, 1024, 0, 0, 1024, 1024]] * batch)}
+    t0 = time.perf_counter()
+    with torch.no_grad():
+        model(x, torch.tensor(999.0), ehs, added_cond_kwargs=added)
+    return time.perf_counter() - t0
+
+
+def run_reference_arm(args):
+    """The reference's CPU path: stock PyTorch fp32 modules on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from basedxl_b200.flops import unet_flops
+    from basedxl_b200.sdxl_unet import sdxl_config
+
+    cores = torch.get_num_threads()
+    model = cpu_unet()
+    sample_hw = 32  # latent 32 x 32 (a 256^2 image) per step: bounded sample of the 128 x 128 workload
+    full_hw = args.height // 8
+    ratio = unet_flops(sdxl_config(), full_hw, full_hw, 2) / unet_flops(sdxl_config(), sample_hw, sample_hw, 2)
+    for _ in range(args.warmup):
+        cpu_forward_seconds(model, sample_hw)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_forward_seconds(model, sample_hw)
+    per_step = (time.perf_counter() - t0) / args.steps
+    value = per_step * ratio * IMAGE_STEPS
+    sample = (f"per step: one UNet forward, CFG batch 2, {sample_hw}x{sample_hw} latent, fp32, stock PyTorch CPU operators; "
+              f"extrapolated to the {full_hw}x{full_hw} latent by algorithmic FLOPs (x{ratio:.1f}) and to {IMAGE_STEPS} steps")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(per_step * ratio * 1e3, 1), "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"SDXL {args.height}x{args.width} UNet loop, 50 Euler steps, CFG batch 2 (CPU path of the reference: PyTorch modules on host cores)"},
+        "cpu_baseline": {"value": round(value, 2), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": round(value, 2), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- main arm
+def run_b200_arm(args):
+    from basedxl_b200 import _lib
+    from basedxl_b200.flops import unet_flops
+    from basedxl_b200.model import BasedXLPipeline
+    from basedxl_b200.sdxl_unet import sdxl_config
+    from basedxl_b200.utils import BasedXLConfig
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    cfg = BasedXLConfig(height=args.height, width=args.width, patch_parallelism=True, use_cfg=True, warmup_steps=4)
+    rank, dev = cfg.rank, torch.device(cfg.device)
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    torch.cuda.set_device(dev)
+    peaks = load_peaks()
+    pipe = BasedXLPipeline.from_config(cfg, seed=0)
+    host = synthetic_inputs(args.height, args.width, pin=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    stream = torch.cuda.current_stream()
+    # ---- device-resident loop -------------------------------------------------
+    lat, ehs, added = pipe.prepare_inputs(**host)
+    pipe.unet.reset()
+    pipe.denoise(lat, ehs, added, IMAGE_STEPS, 5.0, first_step=0, last_step=max(args.warmup, 1))  # untimed warm-up steps
+    barrier()
+    pipe.unet.reset()
+    sampler = ClockSampler(dev.index if dev.index is not None else 0)
+    sampler.start()
+    launches0 = _lib.launches
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    out = pipe.denoise(lat, ehs, added, max(IMAGE_STEPS, args.steps), 5.0, first_step=0, last_step=args.steps)
+    e1.record(stream)
+    barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    launches = _lib.launches - launches0
+    clocks = sampler.stop()
+    _lib.device_status()
+    assert torch.isfinite(out).all(), "non-finite latents"
+    ms_per_step = ms_total / args.steps
+    value = ms_per_step * IMAGE_STEPS / 1e3
+
+    # ---- end to end through the public API, host buffers in, latent out ----------
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    res = pipe(host["prompt_embeds"], host["pooled_prompt_embeds"], host["negative_prompt_embeds"],
+               host["negative_pooled_prompt_embeds"], num_inference_steps=args.steps, guidance_scale=5.0, latents=host["latents"])
+    final = res.latents.to("cpu", non_blocking=False)
+    e1.record(stream)
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1))
+    h2d = sum(v.numel() * v.element_size() for v in host.values())
+    d2h = final.numel() * final.element_size()
+    e2e_value = e2e_ms / args.steps * IMAGE_STEPS / 1e3
+
+    # ---- roofline of the dominant kernel ----------------------------------------------
+    n_strips = cfg.n_device_per_batch
+    roof = gemm_kernel_roofline(dev, n_strips, args.height, args.width, peaks)
+    flops_image = unet_flops(sdxl_config(), args.height // 8, args.width // 8, 2) * IMAGE_STEPS
+    loop_tflops = flops_image / value / 1e12
+    roof["loop"] = {"algorithmic_tflop_per_image": round(flops_image / 1e12, 1), "achieved_tflops_all_gpus": round(loop_tflops, 1),
+                    "frac_of_sustained_peak_x_gpus": round(loop_tflops / (peaks["tflops_sustained"] * world), 4)}
+
+    # ---- CPU baseline on the host cores (rank 0, N = 1 only) --------------------------------
+    cpu = None
+    if world == 1 and not args.skip_cpu:
+        model = cpu_unet(pipe.unet.model.state_dict())
+        secs = cpu_forward_seconds(model, args.height // 8)
+        cpu = {"value": round(secs * IMAGE_STEPS, 1), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+               "sample": f"one UNet forward (CFG batch 2, {args.height // 8}x{args.width // 8} latent, fp32, stock PyTorch CPU operators) = 1/{IMAGE_STEPS} image, {secs:.1f} s; x{IMAGE_STEPS}"}
+        del model
+
+    if rank == 0:
+        par = "1 gpu" if world == 1 else (f"cfg2 x {n_strips} strips" if n_strips > 1 else "cfg2")
+        line = {
+            "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms_per_step, 3), "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"SDXL {args.height}x{args.width} UNet loop: latent 1x4x{args.height // 8}x{args.width // 8}, CFG batch 2, guidance 5.0, 50 Euler steps, 5 synchronous steps then displaced",
+                       "parallelism": par, "l2": "activations and weights per step (5 GB of fp16 weights) exceed L2; no explicit flush in the loop"},
+            "clocks": clocks, "gpu_launches": launches,
+            "e2e": {"value": round(e2e_value, 4), "unit": UNIT, "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps},
+            "roofline": roof,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=IMAGE_STEPS)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--height", type=int, default=1024)
+    ap.add_argument("--width", type=int, default=1024)
+    ap.add_argument("--skip-cpu", action="store_true", help="omit the cpu_baseline leg")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_b200_arm(args)
+
+
+if __name__ == "__main__":
+    main()
