@@ -36,8 +36,9 @@ class BasedXLGroupNorm(BaseModule):
 
         if self.buffer_list is None and self.comm_manager is not None:
             if self.comm_manager.buffer_list is None:
+                # one fp32 moment = 4 // itemsize staging elements (2 for fp16 activations)
                 self.idx = self.comm_manager.register_tensor(
-                    shape=[2, n, groups, 1, 1, 2], torch_dtype=x.dtype, layer_type="gn"
+                    shape=[2, n, groups, 1, 1, 4 // x.element_size()], torch_dtype=x.dtype, layer_type="gn"
                 )
             else:
                 self.buffer_list = [t.view(-1).view(torch.float32) for t in self.comm_manager.get_buffer_list(self.idx)]

@@ -308,7 +308,7 @@ class UNet2DConditionModel(nn.Module):
 
     @property
     def dtype(self):
-        return self.conv_in.weight.dtype
+        return next(self.parameters()).dtype
 
     def embed(self, timestep, batch: int, added_cond_kwargs, device):
         cfg = self.config
