@@ -159,11 +159,14 @@ def halo_pack(x, pad=1, out=None):
 
 
 # --------------------------------------------------------------------------- GroupNorm
-_gn_scratch: dict[tuple[int, int], torch.Tensor] = {}
+_gn_scratch: dict[int, torch.Tensor] = {}
 
 
 def _scratch(device, nbytes: int) -> torch.Tensor:
-    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream())
+    """Per-device scratch for the GroupNorm statistics kernel (zeroed once; the
+    kernel leaves its ticket word at zero).  Calls that share it must be ordered
+    on one stream, which holds for the single compute stream the library runs on."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
     t = _gn_scratch.get(key)
     if t is None or t.numel() < nbytes:
         t = torch.zeros(max(nbytes, 1 << 20), device=device, dtype=torch.uint8)

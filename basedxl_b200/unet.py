@@ -81,6 +81,20 @@ class BasedXLUnet(BaseModel):
                 "CUDA graphs (BasedXLPipeline(..., cuda_graph=True)) instead"
             )
         super().__init__(model, cfg)
+        self.cuda_graph = False
+        self._graphed = None
+
+    def enable_cuda_graph(self, enabled: bool = True):
+        """Replay one captured CUDA graph per denoising step instead of launching
+        ~1200 kernels from Python.  Single-GPU runs capture the whole forward."""
+        self.cuda_graph = enabled
+        self.release_graph()
+
+    def release_graph(self):
+        """Drop the captured step graph (call before destroying the process group)."""
+        if getattr(self, "_graphed", None) is not None:
+            self._graphed.release()
+        self._graphed = None
 
     def patch_linear_layers(self, model: nn.Module):
         for _name, module in model.named_modules():
@@ -151,6 +165,32 @@ class BasedXLUnet(BaseModel):
         s, t, e, a = self._slice_batch(sample, timestep, encoder_hidden_states, added_cond_kwargs)
         return self.model(s, t, e, added_cond_kwargs=a, return_dict=False)[0]
 
+    def _step_multi(self, sample, timestep, encoder_hidden_states, added_cond_kwargs, drain: bool = True):
+        """One step on this rank's strip / CFG half, then the blocking gather of all
+        ranks' output strips (basedxl/unet.py:166-175,185-195).  With ``drain`` the
+        tail of the exchange queue is flushed and every pending gather joined before
+        returning, which makes the step self-contained (what graph replay needs);
+        without it the tail is flushed by the next step's first layer, as in the
+        reference.  Either way every layer sees exactly the previous step's data."""
+        cfg = self.basedxl_config
+        b, c, h, w = sample.shape
+        local = self._run_local(sample, timestep, encoder_hidden_states, added_cond_kwargs).contiguous()
+        if drain and self.comm_manager is not None:
+            self.comm_manager.clear()
+        if self.output_buffer is None:
+            self.output_buffer = torch.empty((b, c, h, w), device=local.device, dtype=local.dtype)
+        if self.buffer_list is None:
+            self.buffer_list = [torch.empty_like(local) for _ in range(cfg.world_size)]
+        dist.all_gather(self.buffer_list, local, async_op=False)
+        n = cfg.n_device_per_batch
+        if cfg.use_cfg:
+            # first half of the ranks = batch row 0, second half = row 1
+            torch.cat(self.buffer_list[:n], dim=2, out=self.output_buffer[0:1])
+            torch.cat(self.buffer_list[n:], dim=2, out=self.output_buffer[1:2])
+        else:
+            torch.cat(self.buffer_list, dim=2, out=self.output_buffer)
+        return self.output_buffer
+
     # ------------------------------------------------------------------ one denoising step
     def forward(self, sample, timestep, encoder_hidden_states, added_cond_kwargs={}, **kwargs):
         torch.cuda.nvtx.range_push("unet::forward")
@@ -160,23 +200,30 @@ class BasedXLUnet(BaseModel):
             self.prepare(sample, timestep, encoder_hidden_states, added_cond_kwargs)
 
         if cfg.world_size == 1:
-            output = self.model(sample, timestep, encoder_hidden_states, added_cond_kwargs=added_cond_kwargs, return_dict=False)[0]
-        else:
-            # every rank computes one strip of one CFG half (or of the whole batch)
-            local = self._run_local(sample, timestep, encoder_hidden_states, added_cond_kwargs).contiguous()
-            if self.output_buffer is None:
-                self.output_buffer = torch.empty((b, c, h, w), device=local.device, dtype=local.dtype)
-            if self.buffer_list is None:
-                self.buffer_list = [torch.empty_like(local) for _ in range(cfg.world_size)]
-            dist.all_gather(self.buffer_list, local, async_op=False)
-            n = cfg.n_device_per_batch
-            if cfg.use_cfg:
-                # basedxl/unet.py:172-174: first half of the ranks = batch row 0, second half = row 1
-                torch.cat(self.buffer_list[:n], dim=2, out=self.output_buffer[0:1])
-                torch.cat(self.buffer_list[n:], dim=2, out=self.output_buffer[1:2])
+            if self.cuda_graph and isinstance(timestep, torch.Tensor):
+                if self._graphed is None:
+                    from .graph import GraphedStep
+
+                    self._graphed = GraphedStep(
+                        lambda s, t, e, a: self.model(s, t, e, added_cond_kwargs=a, return_dict=False)[0]
+                    )
+                output = self._graphed(sample, timestep, encoder_hidden_states, added_cond_kwargs)
             else:
-                torch.cat(self.buffer_list, dim=2, out=self.output_buffer)
-            output = self.output_buffer
+                output = self.model(sample, timestep, encoder_hidden_states, added_cond_kwargs=added_cond_kwargs, return_dict=False)[0]
+        else:
+            # Displaced steps repeat the same launch sequence every step, so they are
+            # replayed from a graph; the synchronous warm-up steps (blocking per-layer
+            # collectives, 5 per image) are launched eagerly.
+            displaced = (not self.patched) or self.counter > cfg.warmup_steps
+            if self.cuda_graph and displaced and isinstance(timestep, torch.Tensor):
+                if self._graphed is None:
+                    from .graph import GraphedStep
+
+                    # no eager rehearsal: it would publish this step's tensors a step early
+                    self._graphed = GraphedStep(self._step_multi, warmup_runs=0)
+                output = self._graphed(sample, timestep, encoder_hidden_states, added_cond_kwargs)
+            else:
+                output = self._step_multi(sample, timestep, encoder_hidden_states, added_cond_kwargs, drain=False)
         self.counter += 1
         torch.cuda.nvtx.range_pop()
         return (output,)

@@ -244,6 +244,8 @@ def run_b200_arm(args):
     torch.cuda.set_device(dev)
     peaks = load_peaks()
     pipe = BasedXLPipeline.from_config(cfg, seed=0)
+    if not args.no_graph:
+        pipe.unet.enable_cuda_graph()
     host = synthetic_inputs(args.height, args.width, pin=True)
 
     def barrier():
@@ -321,16 +323,27 @@ def run_b200_arm(args):
             "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"SDXL {args.height}x{args.width} UNet loop: latent 1x4x{args.height // 8}x{args.width // 8}, CFG batch 2, guidance 5.0, 50 Euler steps, 5 synchronous steps then displaced",
                        "parallelism": par, "l2": "activations and weights per step (5 GB of fp16 weights) exceed L2; no explicit flush in the loop"},
-            "clocks": clocks, "gpu_launches": launches,
+            "clocks": clocks, "gpu_launches": launches, "cuda_graph": bool(pipe.unet.cuda_graph),
             "e2e": {"value": round(e2e_value, 4), "unit": UNIT, "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps},
             "roofline": roof,
         }
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
+    shutdown(pipe, world)
+
+
+def shutdown(pipe, world):
+    """Release captured graphs before the process group goes away; a watchdog ends
+    the process if tear-down stalls, so that a finished run never blocks its launcher."""
+    sys.stdout.flush()
+    threading.Timer(30.0, lambda: os._exit(0)).start()
+    pipe.unet.release_graph()
+    torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    os._exit(0)
 
 
 def main():
@@ -341,6 +354,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--height", type=int, default=1024)
     ap.add_argument("--width", type=int, default=1024)
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the cpu_baseline leg")
     args = ap.parse_args()
     if args.warmup < 3:

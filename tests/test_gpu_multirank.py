@@ -23,7 +23,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, use_cfg, port, ret):
+def _worker(rank, world, use_cfg, graph, port, ret):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(world), RANK=str(rank), LOCAL_RANK=str(rank))
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -43,6 +43,8 @@ def _worker(rank, world, use_cfg, port, ret):
     model.load_state_dict(seeded.state_dict())
     model = model.half().to(dev)
     pipe = BasedXLPipeline(BasedXLUnet(model, cfg), cfg)
+    if graph:
+        pipe.unet.enable_cuda_graph()
     T = lambda k: torch.from_numpy(g[k]).to(dev)
     added = {"text_embeds": T("in_text_embeds").half(), "time_ids": T("in_time_ids")}
     pipe.unet.reset()
@@ -51,7 +53,7 @@ def _worker(rank, world, use_cfg, port, ret):
 
     def spy(*a, **k):
         o = orig(*a, **k)
-        outs.append(o[0].float().cpu())
+        outs.append(o[0].float().clone())
         return o
 
     pipe.unet.forward = spy
@@ -59,10 +61,14 @@ def _worker(rank, world, use_cfg, port, ret):
     pipe.unet.comm_manager.clear()
     torch.cuda.synchronize()
     _lib.device_status()
+    pipe.unet.release_graph()
     if rank == 0:
         ret["final"] = final.float().cpu().numpy()
-        ret["outs"] = torch.stack(outs).numpy()
+        ret["outs"] = torch.stack(outs).cpu().numpy()
     dist.barrier()
+    import threading
+
+    threading.Timer(20.0, lambda: os._exit(0)).start()  # backstop: never let tear-down stall the test
     dist.destroy_process_group()
 
 
@@ -70,13 +76,14 @@ def _rel(a, b):
     return float(np.linalg.norm(a.astype(np.float64) - b) / np.linalg.norm(b.astype(np.float64)))
 
 
+@pytest.mark.parametrize("graph", [False, True], ids=["eager", "graph"])
 @pytest.mark.parametrize("tag,world,use_cfg", [("ws2_nocfg", 2, False), ("ws4_cfg", 4, True), ("ws4_nocfg", 4, False)])
-def test_loop_on_gpus_matches_reference_run(tag, world, use_cfg):
+def test_loop_on_gpus_matches_reference_run(tag, world, use_cfg, graph):
     if not torch.cuda.is_available() or torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     g = np.load(GOLDEN)
     ret = mp.Manager().dict()
-    mp.spawn(_worker, args=(world, use_cfg, _free_port(), ret), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, use_cfg, graph, _free_port(), ret), nprocs=world, join=True)
     per_step = [_rel(ret["outs"][i], g[f"{tag}_outs"][i]) for i in range(STEPS)]
     print(tag, "per-step rel-L2", [f"{e:.2e}" for e in per_step], "final", _rel(ret["final"], g[f"{tag}_latents"]))
     # fp16 kernels against the reference's fp32 CPU run: per-step bar 2e-3, final latents 1e-2
