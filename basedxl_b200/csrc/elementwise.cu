@@ -31,9 +31,9 @@ __global__ void conv3x3_small_cin_kernel(const __half* __restrict__ x, long long
                                          const __half* __restrict__ bot, long long halo_img_stride,
                                          const __half* __restrict__ w, const __half* __restrict__ bias, __half* __restrict__ y,
                                          int B, int Cin, int Cout, int H, int W) {
-  extern __shared__ float s_w[];  // [Cout][9*Cin]
+  extern __shared__ float s_w[];  // [9*Cin][Cout]: threads of a warp (consecutive output vectors) read consecutive words
   const int K = 9 * Cin;
-  for (int i = threadIdx.x; i < Cout * K; i += blockDim.x) s_w[i] = __half2float(w[i]);
+  for (int i = threadIdx.x; i < Cout * K; i += blockDim.x) s_w[(i % K) * Cout + i / K] = __half2float(w[i]);
   __syncthreads();
   const int ovecs = Cout / 8;
   const long long total = (long long)B * H * W * ovecs;
@@ -65,8 +65,10 @@ __global__ void conv3x3_small_cin_kernel(const __half* __restrict__ x, long long
         const int kbase = (ky * 3 + kx) * Cin;
         for (int c = 0; c < Cin; ++c) {
           const float v = __half2float(px[c]);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) acc[j] += v * s_w[(ov * 8 + j) * K + kbase + c];
+          const float4 w0 = *reinterpret_cast<const float4*>(&s_w[(kbase + c) * Cout + ov * 8]);
+          const float4 w1 = *reinterpret_cast<const float4*>(&s_w[(kbase + c) * Cout + ov * 8 + 4]);
+          acc[0] += v * w0.x, acc[1] += v * w0.y, acc[2] += v * w0.z, acc[3] += v * w0.w;
+          acc[4] += v * w1.x, acc[5] += v * w1.y, acc[6] += v * w1.z, acc[7] += v * w1.w;
         }
       }
     }
@@ -290,7 +292,7 @@ extern "C" int bxl_conv3x3_direct_f16(const void* x, long long x_img_stride, con
     }
     const long long total = (long long)B * H * W * (C_out / 8);
     int blocks = grid_for(total, 256);
-    if (blocks > sm_count() * 2) blocks = sm_count() * 2;  // weights are staged per CTA
+    if (blocks > sm_count() * 4) blocks = sm_count() * 4;  // weights are staged once per CTA
     conv3x3_small_cin_kernel<<<blocks, 256, smem, s>>>(static_cast<const __half*>(x), x_img_stride,
                                                        static_cast<const __half*>(top), static_cast<const __half*>(bot),
                                                        halo_img_stride, static_cast<const __half*>(w_packed),

@@ -12,6 +12,13 @@
 //               convert and store; runs while the next tile's mainloop fills the
 //               other accumulator buffer (two TMEM buffers of BN columns)
 //
+// Tile width BN (32..256) and an optional K split are chosen per problem by the
+// host.  With a K split of S, the S CTAs of a thread-block cluster each run 1/S
+// of the K loop of the same tile and reduce through distributed shared memory:
+// every CTA owns BN/S output columns, receives the peers' fp32 partial sums for
+// them by remote shared-memory stores, adds its own accumulator and stores.  This
+// keeps all SMs busy when a strip's problem has only a handful of tiles.
+//
 // Roofline: tensor cores.  Algorithmic FLOPs per tile = 2*128*BN*K.
 #include "bxl_common.cuh"
 #include "bxl_host.h"
@@ -24,6 +31,10 @@ constexpr int kBK = 64;            // K per stage: 64 fp16 = one 128-byte swizzl
 constexpr int kUmmaK = 16;         // K of one tcgen05.mma.kind::f16
 constexpr int kGemmThreads = 192;
 constexpr int kMaxSeg = 3;
+constexpr int kABytes = kBM * kBK * 2;       // 16 KB
+constexpr int kSmemBudget = 227 * 1024;      // dynamic shared memory available to one CTA
+constexpr int kSmemMisc = 2048;              // alignment slack + barriers
+constexpr int kMaxStages = 8;
 
 struct alignas(64) GemmParams {
   CUtensorMap a_map[kMaxSeg];  // GEMM: A of each segment.  conv: body, top halo, bottom halo
@@ -32,6 +43,10 @@ struct alignas(64) GemmParams {
   int M, N, K;                 // conv: M = B*H_out*W_out (unused), N = C_out, K = 9*C_in
   int nseg;                    // GEMM segments (1, or 3 for the split-operand product)
   int b_kn;                    // B given as [K,N] row-major (MN-major operand) instead of [N,K]
+  // tiling chosen by the host
+  int bn;                      // tile width: multiple of 32, 32..256
+  int split;                   // K split over a cluster of `split` CTAs (1, 2 or 4)
+  int stages;                  // depth of the operand ring
   // epilogue
   const __half* bias;          // [N] or null
   const __half* bias_rows;     // conv only: [B][N] per-image bias (time embedding) or null
@@ -48,37 +63,102 @@ struct alignas(64) GemmParams {
   int* dev_status;
 };
 
-template <int BN>
-struct GemmSmem {
-  static constexpr int kABytes = kBM * kBK * 2;            // 16 KB
-  static constexpr int kBBytes = BN * kBK * 2;             // 16 / 32 KB
-  static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
-  static constexpr int kBarBytes = 1024;
-  static constexpr int kTotal = kStages * kStageBytes + kBarBytes + 1024;  // + alignment slack
-};
+// Split-K exchange buffer of one CTA: for each of the (split-1) peers, the fp32
+// partial sums of this CTA's column slice, stored [16-byte chunk][row] so that the
+// 32 rows a warp writes (or reads) at once are contiguous.
+__host__ __device__ inline int recv_bytes(int bn, int split) { return split > 1 ? (split - 1) * (bn / split) * kBM * 4 : 0; }
 
-template <int BN, bool kConv>
+// Bias, per-image bias, residual, conversion and the global store of 32 consecutive
+// output columns [nb, nb+32) of one output row.
+template <bool kConv>
+__device__ __forceinline__ void store_chunk(const GemmParams& p, float (&f)[32], long long out_row, int nb, int img) {
+  const bool fullw = (nb + 32 <= p.N);
+  if (p.bias) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (fullw || nb + j < p.N) f[j] += __half2float(p.bias[nb + j]);
+  }
+  if (kConv && p.bias_rows) {
+    const __half* br = p.bias_rows + static_cast<long long>(img) * p.N;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (fullw || nb + j < p.N) f[j] += __half2float(br[nb + j]);
+  }
+  if (p.residual) {
+    const __half* rr = p.residual + out_row * p.ldr + nb;
+    if (fullw) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint4 u = *reinterpret_cast<const uint4*>(rr + q * 8);
+        const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 g = __half22float2(h[j]);
+          f[q * 8 + 2 * j] += g.x;
+          f[q * 8 + 2 * j + 1] += g.y;
+        }
+      }
+    } else {
+      for (int j = 0; j < 32; ++j)
+        if (nb + j < p.N) f[j] += __half2float(rr[j]);
+    }
+  }
+  if (p.out_f32) {
+    float* cr = static_cast<float*>(p.C) + out_row * p.ldc + nb;
+    if (fullw) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        *reinterpret_cast<float4*>(cr + q * 4) = make_float4(f[q * 4], f[q * 4 + 1], f[q * 4 + 2], f[q * 4 + 3]);
+    } else {
+      for (int j = 0; j < 32; ++j)
+        if (nb + j < p.N) cr[j] = f[j];
+    }
+  } else {
+    __half* cr = static_cast<__half*>(p.C) + out_row * p.ldc + nb;
+    if (fullw) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 u;
+        __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(f[q * 8 + 2 * j], f[q * 8 + 2 * j + 1]);
+        *reinterpret_cast<uint4*>(cr + q * 8) = u;
+      }
+    } else {
+      for (int j = 0; j < 32; ++j)
+        if (nb + j < p.N) cr[j] = __float2half_rn(f[j]);
+    }
+  }
+}
+
+template <bool kConv>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid_constant__ GemmParams p) {
-  using S = GemmSmem<BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t bar_base = smem_base + S::kStages * S::kStageBytes;
-  // barrier layout (8 bytes each): full[kStages], empty[kStages], tfull[2], tempty[2]
+  const int BN = p.bn;
+  const int S = p.split;
+  const int stage_bytes = kABytes + BN * 128;
+  const uint32_t recv_base = smem_base + p.stages * stage_bytes;            // 1024-aligned (stage_bytes % 1024 == 0)
+  const uint32_t bar_base = recv_base + recv_bytes(BN, S);
+  // barriers (8 bytes each): full[kMaxStages], empty[kMaxStages], tfull[2], tempty[2], recv_full, recv_free
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (S::kStages + s); };
-  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * S::kStages + a); };
-  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * S::kStages + 2 + a); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + S::kStages * S::kStageBytes + 512);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + S::kStages * S::kStageBytes + 520);
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + 2 + a); };
+  const uint32_t recv_full_bar = bar_base + 8u * (2 * kMaxStages + 4);
+  const uint32_t recv_free_bar = bar_base + 8u * (2 * kMaxStages + 5);
+  uint8_t* misc = smem_gen + (bar_base - smem_base) + 256;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(misc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 8);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  constexpr uint32_t kTmemCols = 2 * BN;  // 256 or 512: a power of two >= 32
+  const uint32_t tmem_cols = (2 * BN <= 64) ? 64u : (2 * BN <= 128) ? 128u : (2 * BN <= 256) ? 256u : 512u;
+  const uint32_t crank = (S > 1) ? cluster_ctarank() : 0u;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < S::kStages; ++s) {
+    for (int s = 0; s < p.stages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
@@ -86,15 +166,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
     }
+    const uint32_t peers_threads = (S > 1) ? (S - 1) * 128u : 1u;  // every epilogue thread of every peer
+    mbar_init(recv_full_bar, peers_threads);
+    mbar_init(recv_free_bar, peers_threads);
     *abort_flag = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), tmem_cols);
     tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (S > 1) cluster_sync_all();  // peers' barriers are initialised before anyone arrives on them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -106,6 +190,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
   const int num_tiles = tiles_m * tiles_n;
   const int kb_per_seg = kConv ? 9 * (p.cCin / kBK) : (p.K + kBK - 1) / kBK;
   const int num_kb = kConv ? kb_per_seg : kb_per_seg * p.nseg;
+  // this CTA's share of the K loop (balanced; never empty because split <= num_kb)
+  const int kb_begin = static_cast<int>((static_cast<long long>(crank) * num_kb) / S);
+  const int kb_end = static_cast<int>((static_cast<long long>(crank + 1) * num_kb) / S);
+  const int first_tile = blockIdx.x / S;
+  const int tile_step = gridDim.x / S;
 
   if (warp == 0) {
     // ======================= TMA producer =======================
@@ -117,7 +206,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
         const int tm = tile % tiles_m;
         const int tn = tile / tiles_m;
         const int n0 = tn * BN;
@@ -129,14 +218,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
           y0 = (r / p.tiles_x) * p.th;
           x0 = (r % p.tiles_x) * p.tw;
         }
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.dev_status, 100)) {
             ok = false;
             break;
           }
-          const uint32_t a_dst = smem_base + stage * S::kStageBytes;
-          const uint32_t b_dst = a_dst + S::kABytes;
-          mbar_arrive_expect_tx(full_bar(stage), S::kStageBytes);
+          const uint32_t a_dst = smem_base + stage * stage_bytes;
+          const uint32_t b_dst = a_dst + kABytes;
+          mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
           if (kConv) {
             const int cchunks = p.cCin / kBK;
             const int tap = kb / cchunks;
@@ -174,7 +263,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
               tma_load_2d(b_dst, &p.b_map[seg], full_bar(stage), k0, n0);
             }
           }
-          if (++stage == S::kStages) {
+          if (++stage == p.stages) {
             stage = 0;
             phase ^= 1u;
           }
@@ -189,35 +278,36 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1u;
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.dev_status, 200)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag, p.dev_status, 201)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t a_addr = smem_base + stage * S::kStageBytes;
-          const uint32_t b_addr = a_addr + S::kABytes;
+          const uint32_t a_addr = smem_base + stage * stage_bytes;
+          const uint32_t b_addr = a_addr + kABytes;
           const uint64_t adesc = make_smem_desc_sw128(a_addr, 16, 1024);
+          const uint32_t first = (kb == kb_begin) ? 0u : 1u;
           if (!kConv && p.b_kn) {
             // MN-major B: 64-column chunks 8 KB apart (LBO), 8-row k-groups 1 KB apart (SBO)
             const uint64_t bdesc = make_smem_desc_sw128(b_addr, 8192, 1024);
 #pragma unroll
             for (int k = 0; k < kBK / kUmmaK; ++k)
-              umma_f16(d_tmem, adesc + 2u * k, bdesc + 128u * k, idesc, (kb | k) != 0);
+              umma_f16(d_tmem, adesc + 2u * k, bdesc + 128u * k, idesc, first | k);
           } else {
             const uint64_t bdesc = make_smem_desc_sw128(b_addr, 16, 1024);
 #pragma unroll
             for (int k = 0; k < kBK / kUmmaK; ++k)
-              umma_f16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0);
+              umma_f16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, first | k);
           }
           umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
-          if (++stage == S::kStages) {
+          if (++stage == p.stages) {
             stage = 0;
             phase ^= 1u;
           }
@@ -229,8 +319,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
     // ======================= epilogue (warps 2..5) =======================
     const int quarter = warp & 3;  // TMEM lane quarter this warp may access
     const int row_in_tile = quarter * 32 + lane;
+    const int chunks = BN / 32;
+    const int cps = chunks / S;    // 32-column chunks per owner slice
     int it = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+    for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
       const int tm = tile % tiles_m;
@@ -250,76 +342,72 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
         if (m < p.M) out_row = m;
       }
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.dev_status, 300)) break;
+      __syncwarp();
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      if (S == 1) {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_row + c * 32, v);
-        tmem_ld_wait();
-        const int nb = n0 + c * 32;
-        if (out_row >= 0 && nb < p.N) {
+        for (int c = 0; c < chunks; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_row + c * 32, v);
+          tmem_ld_wait();
+          const int nb = n0 + c * 32;
+          if (out_row >= 0 && nb < p.N) {
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+            store_chunk<kConv>(p, f, out_row, nb, img);
+          }
+        }
+      } else {
+        // ---- split-K: push the partial sums of the peers' column slices into their
+        //      exchange buffers, then reduce and store this CTA's own slice ----
+        // peers must have finished reading what was pushed for the previous tile
+        if (it > 0 && !mbar_wait_cluster(recv_free_bar, (it - 1) & 1u, abort_flag, p.dev_status, 301)) break;
+        __syncwarp();
+#pragma unroll 1
+        for (int c = 0; c < chunks; ++c) {
+          const uint32_t owner = c / cps;
+          if (owner == crank) continue;
+          uint32_t v[32];
+          tmem_ld_32x32(t_row + c * 32, v);
+          tmem_ld_wait();
+          const uint32_t slot = (crank < owner) ? crank : crank - 1;   // this CTA's slot at the owner
+          const uint32_t base = recv_base + ((slot * cps + (c % cps)) * 8u * kBM + row_in_tile) * 16u;
+          const uint32_t remote = map_to_cta(base, owner);
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            st_cluster_f32x4(remote + q * kBM * 16u, __uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                             __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+        }
+        for (uint32_t o = 0; o < static_cast<uint32_t>(S); ++o)
+          if (o != crank) mbar_arrive_remote(map_to_cta(recv_full_bar, o));
+        // own slice: wait for every peer's partials
+        if (!mbar_wait_cluster(recv_full_bar, it & 1u, abort_flag, p.dev_status, 302)) break;
+        __syncwarp();
+#pragma unroll 1
+        for (int cc = 0; cc < cps; ++cc) {
+          const int c = crank * cps + cc;
+          uint32_t v[32];
+          tmem_ld_32x32(t_row + c * 32, v);
+          tmem_ld_wait();
           float f[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-          const bool fullw = (nb + 32 <= p.N);
-          if (p.bias) {
+          for (int slot = 0; slot < S - 1; ++slot) {
+            const uint8_t* src = smem_gen + (recv_base - smem_base) + ((slot * cps + cc) * 8 * kBM + row_in_tile) * 16;
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (fullw || nb + j < p.N) f[j] += __half2float(p.bias[nb + j]);
-          }
-          if (kConv && p.bias_rows) {
-            const __half* br = p.bias_rows + static_cast<long long>(img) * p.N;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (fullw || nb + j < p.N) f[j] += __half2float(br[nb + j]);
-          }
-          if (p.residual) {
-            const __half* rr = p.residual + out_row * p.ldr + nb;
-            if (fullw) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const uint4 u = *reinterpret_cast<const uint4*>(rr + q * 8);
-                const __half2* h = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const float2 g = __half22float2(h[j]);
-                  f[q * 8 + 2 * j] += g.x;
-                  f[q * 8 + 2 * j + 1] += g.y;
-                }
-              }
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (nb + j < p.N) f[j] += __half2float(rr[j]);
+            for (int q = 0; q < 8; ++q) {
+              const float4 g = *reinterpret_cast<const float4*>(src + q * kBM * 16);
+              f[4 * q] += g.x, f[4 * q + 1] += g.y, f[4 * q + 2] += g.z, f[4 * q + 3] += g.w;
             }
           }
-          if (p.out_f32) {
-            float* cr = static_cast<float*>(p.C) + out_row * p.ldc + nb;
-            if (fullw) {
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                *reinterpret_cast<float4*>(cr + q * 4) = make_float4(f[q * 4], f[q * 4 + 1], f[q * 4 + 2], f[q * 4 + 3]);
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (nb + j < p.N) cr[j] = f[j];
-            }
-          } else {
-            __half* cr = static_cast<__half*>(p.C) + out_row * p.ldc + nb;
-            if (fullw) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                uint4 u;
-                __half2* h = reinterpret_cast<__half2*>(&u);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(f[q * 8 + 2 * j], f[q * 8 + 2 * j + 1]);
-                *reinterpret_cast<uint4*>(cr + q * 8) = u;
-              }
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (nb + j < p.N) cr[j] = __float2half_rn(f[j]);
-            }
-          }
+          const int nb = n0 + c * 32;
+          if (out_row >= 0 && nb < p.N) store_chunk<kConv>(p, f, out_row, nb, img);
         }
+        // tell the peers their pushes have been consumed
+        for (uint32_t o = 0; o < static_cast<uint32_t>(S); ++o)
+          if (o != crank) mbar_arrive_remote(map_to_cta(recv_free_bar, o));
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -337,42 +425,97 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
     while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
     __syncthreads();
   }
+  // no CTA of a cluster may leave while a peer can still write into its shared memory
+  if (S > 1) cluster_sync_all();
   if (warp == 1) {
+    __syncwarp();
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc(tmem_base, tmem_cols);
   }
 }
 
 // ---------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------
-template <int BN, bool kConv>
+struct TileConfig {
+  int bn, split, stages;
+};
+
+static int stages_for(int bn, int split) {
+  const int stage = kABytes + bn * 128;
+  int st = (kSmemBudget - kSmemMisc - recv_bytes(bn, split)) / stage;
+  if (st > kMaxStages) st = kMaxStages;
+  return st;
+}
+
+// Pick the tile width and the K split that minimise a simple time model, in units
+// of one 128-column k-block: rounds x (k-blocks per unit x cost(bn) + epilogue) + fill.
+// A wider tile moves fewer operand bytes per FLOP; a narrower one or a K split
+// fills more of the SMs when the problem has few tiles.
+static TileConfig choose_tiles(int tiles_m, int N, int num_kb, bool b_kn, int force_bn = 0, int force_split = 0) {
+  const int sms = sm_count();
+  TileConfig best{128, 1, stages_for(128, 1)};
+  double best_cost = 1e30;
+  for (int bn = 32; bn <= 256; bn += 32) {
+    if (b_kn && bn % 64) continue;            // MN-major B is loaded in 64-column boxes
+    if (force_bn && bn != force_bn) continue;
+    const int tiles = tiles_m * ((N + bn - 1) / bn);
+    for (int split = 1; split <= 4; split *= 2) {
+      if (force_split && split != force_split) continue;
+      if ((bn / 32) % split || split > num_kb) continue;
+      const int st = stages_for(bn, split);
+      if (st < 3) continue;
+      const int clusters = sms / split;
+      const int par = tiles < clusters ? tiles : clusters;
+      const int rounds = (tiles + par - 1) / par;
+      const double kb_cost = 0.30 + 0.70 * bn / 128.0;
+      const double kb_unit = (num_kb + split - 1) / split;
+      const double epi = (bn / 128.0) * 3.0 / split + (split > 1 ? 3.0 : 0.0);
+      const double cost = rounds * (kb_unit * kb_cost + epi) + 8.0;
+      if (cost < best_cost - 1e-9) {
+        best_cost = cost;
+        best = TileConfig{bn, split, st};
+      }
+    }
+  }
+  return best;
+}
+
+template <bool kConv>
 static int launch(const GemmParams& p, int num_tiles, cudaStream_t stream) {
-  using S = GemmSmem<BN>;
+  const int smem = p.stages * (kABytes + p.bn * 128) + recv_bytes(p.bn, p.split) + kSmemMisc;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    if (int rc = check_cuda(cudaFuncSetAttribute(gemm_conv_kernel<BN, kConv>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 S::kTotal),
+    if (int rc = check_cuda(cudaFuncSetAttribute(gemm_conv_kernel<kConv>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget),
                             "cudaFuncSetAttribute(gemm)"))
       return rc;
     configured[dev] = true;
   }
-  int grid = sm_count();
-  if (grid > num_tiles) grid = num_tiles;
-  if (grid < 1) grid = 1;
-  gemm_conv_kernel<BN, kConv><<<grid, kGemmThreads, S::kTotal, stream>>>(p);
-  return check_cuda(cudaGetLastError(), "gemm_conv_kernel launch");
-}
-
-// tile width: fewest wasted columns, ties to the wider tile
-static int pick_bn(int N) {
-  const int t128 = (N + 127) / 128 * 128, t256 = (N + 255) / 256 * 256;
-  return (t256 <= t128) ? 256 : 128;
+  int clusters = sm_count() / p.split;
+  if (clusters > num_tiles) clusters = num_tiles;
+  if (clusters < 1) clusters = 1;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(clusters * p.split);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = p.split;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.split > 1 ? 1 : 0;
+  return check_cuda(cudaLaunchKernelEx(&cfg, gemm_conv_kernel<kConv>, p), "gemm_conv_kernel launch");
 }
 
 static int aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// test hook: force the tile width / K split (0 = choose)
+static int g_force_bn = 0, g_force_split = 0;
 
 }  // namespace bxl
 
@@ -393,7 +536,9 @@ extern "C" int bxl_gemm_f16(const void* A, long long lda, const void* B, long lo
   if (!st) return fail(kErrCuda, "bxl_gemm_f16: no device status word");
   GemmParams p;
   memset(&p, 0, sizeof(p));
-  const int BN = pick_bn(N);
+  const int tiles_m = (M + kBM - 1) / kBM;
+  const TileConfig tc = choose_tiles(tiles_m, N, (K + kBK - 1) / kBK, b_is_kn != 0, g_force_bn, g_force_split);
+  const int BN = tc.bn;
   {
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
     uint64_t str[1] = {(uint64_t)lda * 2};
@@ -416,12 +561,20 @@ extern "C" int bxl_gemm_f16(const void* A, long long lda, const void* B, long lo
     p.b_map[s] = p.b_map[0];
   }
   p.M = M, p.N = N, p.K = K, p.nseg = 1, p.b_kn = b_is_kn ? 1 : 0;
+  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages;
   p.bias = static_cast<const __half*>(bias);
   p.residual = static_cast<const __half*>(residual);
   p.ldr = ldr, p.C = C, p.ldc = ldc, p.out_f32 = out_f32 ? 1 : 0;
   p.dev_status = st;
-  const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
-  return BN == 256 ? launch<256, false>(p, tiles, (cudaStream_t)stream) : launch<128, false>(p, tiles, (cudaStream_t)stream);
+  const int tiles = tiles_m * ((N + BN - 1) / BN);
+  return launch<false>(p, tiles, (cudaStream_t)stream);
+}
+
+extern "C" int bxl_debug_force_tiles(int bn, int split) {
+  if (bn < 0 || bn > 256 || bn % 32 || (split != 0 && split != 1 && split != 2 && split != 4))
+    return fail(kErrInvalidArg, "bxl_debug_force_tiles: bn must be 0 or a multiple of 32 up to 256, split 0, 1, 2 or 4");
+  g_force_bn = bn, g_force_split = split;
+  return kOk;
 }
 
 // ---- split-operand product of fp32 matrices ---------------------------------------
@@ -467,7 +620,9 @@ extern "C" int bxl_gemm_split_f32(const float* A, const float* B, float* C, int 
   if (int rc = check_cuda(cudaGetLastError(), "split_f32_kernel launch")) return rc;
   GemmParams p;
   memset(&p, 0, sizeof(p));
-  const int BN = pick_bn(N);
+  const int tiles_m = (M + kBM - 1) / kBM;
+  const TileConfig tc = choose_tiles(tiles_m, N, 3 * ((K + kBK - 1) / kBK), true, g_force_bn, g_force_split);
+  const int BN = tc.bn;
   // C = A_hi*B_hi + A_hi*B_lo + A_lo*B_hi, one fp32 accumulator
   const __half* as[3] = {a_hi, a_hi, a_lo};
   const __half* bs[3] = {b_hi, b_lo, b_hi};
@@ -482,10 +637,11 @@ extern "C" int bxl_gemm_split_f32(const float* A, const float* B, float* C, int 
     if (int rc = encode_tmap_f16(&p.b_map[i], bs[i], 2, bd, bstr, bbox)) return rc;
   }
   p.M = M, p.N = N, p.K = K, p.nseg = 3, p.b_kn = 1;
+  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages;
   p.C = C, p.ldc = N, p.out_f32 = 1;
   p.dev_status = st;
-  const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
-  return BN == 256 ? launch<256, false>(p, tiles, s) : launch<128, false>(p, tiles, s);
+  const int tiles = tiles_m * ((N + BN - 1) / BN);
+  return launch<false>(p, tiles, s);
 }
 
 // ---- convolution --------------------------------------------------------------------
@@ -543,7 +699,9 @@ extern "C" int bxl_conv3x3_halo_f16(const void* x, long long x_img_stride, const
   if (int rc = enc(&p.a_map[1], top ? top : x, 1, top ? halo_img_stride : x_img_stride)) return rc;
   if (int rc = enc(&p.a_map[2], bot ? bot : x, 1, bot ? halo_img_stride : x_img_stride)) return rc;
   const int K = 9 * C_in;
-  const int BN = pick_bn(C_out);
+  const int tiles_x = (W_out + tw - 1) / tw, tiles_y = (H_out + th - 1) / th;
+  const TileConfig tc = choose_tiles(B * tiles_x * tiles_y, C_out, K / kBK, false, g_force_bn, g_force_split);
+  const int BN = tc.bn;
   {
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)C_out};
     uint64_t str[1] = {(uint64_t)K * 2};
@@ -553,15 +711,16 @@ extern "C" int bxl_conv3x3_halo_f16(const void* x, long long x_img_stride, const
   p.b_map[1] = p.b_map[0];
   p.b_map[2] = p.b_map[0];
   p.M = B * H_out * W_out, p.N = C_out, p.K = K, p.nseg = 1, p.b_kn = 0;
+  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages;
   p.bias = static_cast<const __half*>(bias);
   p.bias_rows = static_cast<const __half*>(bias_rows);
   p.residual = static_cast<const __half*>(residual);
   p.ldr = C_out, p.C = y, p.ldc = C_out, p.out_f32 = 0;
   p.cB = B, p.cHin = H_in, p.cW = W, p.cCin = C_in, p.cStride = stride, p.cHout = H_out, p.cWout = W_out;
   p.tw = tw, p.th = th;
-  p.tiles_x = (W_out + tw - 1) / tw, p.tiles_y = (H_out + th - 1) / th;
+  p.tiles_x = tiles_x, p.tiles_y = tiles_y;
   p.has_top = top ? 1 : 0, p.has_bot = bot ? 1 : 0;
   p.dev_status = st;
-  const int tiles = B * p.tiles_x * p.tiles_y * ((C_out + BN - 1) / BN);
-  return BN == 256 ? launch<256, true>(p, tiles, (cudaStream_t)stream) : launch<128, true>(p, tiles, (cudaStream_t)stream);
+  const int tiles = B * tiles_x * tiles_y * ((C_out + BN - 1) / BN);
+  return launch<true>(p, tiles, (cudaStream_t)stream);
 }

@@ -40,6 +40,11 @@ int bxl_device_status(int* code, int* site, int* block);
 
 int bxl_sm_count(void);
 
+/* Test hook: force the GEMM / convolution tile width (multiple of 32, <= 256) and
+ * K split (1, 2 or 4); 0 restores the built-in choice.  No counterpart in the
+ * reference. */
+int bxl_debug_force_tiles(int bn, int split);
+
 /* ---- matmul ------------------------------------------------------------- */
 
 /* C[M,N] = A[M,K] * B (+ bias[N]) (+ residual[M,N]); fp16 operands, fp32

@@ -166,3 +166,27 @@ def test_halo_pack_is_bit_exact():
     ref = po.conv2d_boundary(x, 1)  # [2, B, C, 1, W]
     assert torch.equal(packed.cpu().permute(0, 1, 4, 2, 3), ref)
     _lib.device_status()
+
+
+@pytest.mark.parametrize("bn,split", [(64, 1), (160, 1), (256, 1), (128, 2), (128, 4), (256, 4)])
+def test_conv_forced_tile_width_and_k_split(bn, split):
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    gen = torch.Generator().manual_seed(bn + split)
+    x = h16(torch.randn(2, 128, 16, 32, generator=gen))
+    xp = h16(x + 0.01 * torch.randn(2, 128, 16, 32, generator=gen))
+    w = h16(torch.randn(320, 128, 3, 3, generator=gen) / 34)
+    b = h16(torch.randn(320, generator=gen))
+    xs, xps = torch.chunk(x, 2, 2), torch.chunk(xp, 2, 2)
+    stale = [po.conv2d_boundary(t, 1) for t in xps]
+    l = _lib.lib()
+    _lib.check(l.bxl_debug_force_tiles(bn, split), l, kernels=0)
+    try:
+        for i in range(2):
+            ref = po.conv2d_pp(xs[i], w, b, 1, 1, stale, i, 2)
+            top, bot = _halo_rows(ops, dev, stale, i, 2)
+            y = _conv(ops, dev, xs[i], w, b, 1, top, bot)
+            _lib.device_status()
+            assert_close(y, ref, what=f"conv bn={bn} split={split} strip {i}")
+    finally:
+        _lib.check(l.bxl_debug_force_tiles(0, 0), l, kernels=0)

@@ -107,3 +107,28 @@ def test_bad_arguments_are_rejected():
     w = torch.zeros(128, 68, device=dev, dtype=torch.float16)
     with pytest.raises(_lib.BxlError):
         ops.gemm(a, w)
+
+
+@pytest.mark.parametrize("bn,split", [(32, 1), (64, 1), (96, 1), (160, 1), (192, 1), (224, 1), (256, 1), (64, 2), (128, 2), (128, 4), (256, 2), (256, 4)])
+@pytest.mark.parametrize("M,K,N,b_is_kn", [(300, 1280, 1280, False), (1024, 640, 5120, False), (256, 5120, 1280, False), (384, 704, 640, True)])
+def test_forced_tile_width_and_k_split(M, K, N, b_is_kn, bn, split):
+    """Every tile width and cluster K split gives the same product (several tiles per
+    cluster, so the exchange buffers are reused)."""
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    if b_is_kn and bn % 64:
+        pytest.skip("[K,N] operands are loaded in 64-column boxes")
+    g = torch.Generator().manual_seed(M + K + N + bn + split)
+    a = torch.randn(M, K, generator=g)
+    w = torch.randn(N, K, generator=g) / K**0.5
+    bias, res = torch.randn(N, generator=g), torch.randn(M, N, generator=g)
+    ref = h16(a) @ h16(w).t() + h16(bias) + h16(res)
+    l = _lib.lib()
+    _lib.check(l.bxl_debug_force_tiles(bn, split), l, kernels=0)
+    try:
+        y = ops.gemm(a.half().to(dev), (w.t().contiguous() if b_is_kn else w).half().to(dev), bias=bias.half().to(dev),
+                     residual=res.half().to(dev), b_is_kn=b_is_kn)
+        _lib.device_status()
+    finally:
+        _lib.check(l.bxl_debug_force_tiles(0, 0), l, kernels=0)
+    assert_close(y, ref, what=f"gemm bn={bn} split={split}")
