@@ -243,3 +243,51 @@ extern "C" int bxl_groupnorm_apply_f16(const void* x, void* y, long long img_str
       mode == 0 ? 0 : n_peers, own, mode, eps, static_cast<const __half*>(gamma), static_cast<const __half*>(beta), silu, parts);
   return check_cuda(cudaGetLastError(), "groupnorm_apply_kernel launch");
 }
+
+// ---- statistics without caller-provided scratch ------------------------------------
+// Some hosts of this library cannot hand it device memory at call time: an
+// inference server that reserved its whole memory budget up front and forbids
+// cudaMalloc inside operator callbacks (it may fail, and it synchronises the whole
+// device), or a plugin invoked by a runtime that only passes input and output
+// pointers.  For them the scratch of the statistics kernel lives in this
+// file-scope device array, present once on every GPU that loads the library, for
+// the life of the process.
+namespace bxl {
+constexpr int kGnStaticMaxBG = 256;  // largest images x groups product served
+constexpr long long kGnStaticBytes = 256 + (long long)kGnStaticMaxBG * kGnMaxParts * 2 * sizeof(float);  // 262,400 B
+static __device__ __align__(256) unsigned char g_gn_static_scratch[kGnStaticBytes];
+// device address of the array, per device (the symbol itself is only a host-side handle)
+static void* g_gn_static_ptr[64] = {};
+}  // namespace bxl
+
+extern "C" long long bxl_groupnorm_stats_noalloc_max_bg(void) { return kGnStaticMaxBG; }
+
+extern "C" int bxl_groupnorm_stats_noalloc_f16(const void* x, long long img_stride, int B, int HW, int C, int G,
+                                               float* moments, void* stream) {
+  if (int rc = gn_check("bxl_groupnorm_stats_noalloc_f16", x, B, HW, C, G, img_stride)) return rc;
+  if (!moments) return fail(kErrInvalidArg, "bxl_groupnorm_stats_noalloc_f16: null output");
+  if ((long long)B * G > kGnStaticMaxBG)
+    return fail(kErrTooLarge,
+                "bxl_groupnorm_stats_noalloc_f16: B*G = %lld exceeds the built-in scratch (B*G <= %d); use "
+                "bxl_groupnorm_stats_f16 with caller-owned scratch",
+                (long long)B * G, kGnStaticMaxBG);
+  int dev = 0;
+  if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+  if (dev < 0 || dev >= 64) return fail(kErrUnsupported, "bxl_groupnorm_stats_noalloc_f16: device index %d", dev);
+  if (!g_gn_static_ptr[dev]) {
+    // first call on this device: resolve the array's device address (current device)
+    void* ptr = nullptr;
+    if (int rc = check_cuda(cudaGetSymbolAddress(&ptr, g_gn_static_scratch), "cudaGetSymbolAddress(static scratch)")) return rc;
+    g_gn_static_ptr[dev] = ptr;
+  }
+  char* scratch = static_cast<char*>(g_gn_static_ptr[dev]);
+  cudaStream_t s = (cudaStream_t)stream;
+  // the ticket word must start at zero whatever an earlier call left behind
+  if (int rc = check_cuda(cudaMemsetAsync(scratch, 0, 256, s), "clear ticket")) return rc;
+  const int threads = gn_threads(C), parts = gn_parts(HW, C, B);
+  groupnorm_stats_kernel<<<dim3(parts, B), threads, 2 * C * sizeof(float), s>>>(
+      static_cast<const __half*>(x), img_stride, HW, C, G, parts, reinterpret_cast<float*>(scratch + 256),
+      reinterpret_cast<int*>(scratch), moments, B);
+  return check_cuda(cudaGetLastError(), "groupnorm_stats_kernel launch (static scratch)");
+}
+

@@ -113,6 +113,20 @@ long long bxl_groupnorm_scratch_bytes(int B, int G);
 int bxl_groupnorm_stats_f16(const void* x, long long img_stride, int B, int HW, int C, int G, float* moments,
                             void* scratch, long long scratch_bytes, void* stream);
 
+/* Same result as bxl_groupnorm_stats_f16, for callers that cannot pass scratch
+ * memory (hosts that reserved all device memory up front or whose operator
+ * callbacks may not call cudaMalloc).  This entry point has no counterpart in the
+ * reference.  The scratch is a 262,400-byte array built into the library and
+ * resident on every GPU that loads it; it serves B*G <= 256
+ * (bxl_groupnorm_stats_noalloc_max_bg()), larger problems are rejected with an
+ * error.  Allocates nothing.  The first call on each device looks up the array's
+ * device address and should therefore be made before any stream capture begins.
+ * All calls share the one array: two calls whose kernels may overlap on the GPU
+ * (different streams without ordering) race. */
+long long bxl_groupnorm_stats_noalloc_max_bg(void);
+int bxl_groupnorm_stats_noalloc_f16(const void* x, long long img_stride, int B, int HW, int C, int G, float* moments,
+                                    void* stream);
+
 /* y = GroupNorm(x) (* sigmoid, if silu) using
  *   mode 0: the strip's own moments                         (groupnorm.py:44-45)
  *   mode 1: the average of all peers' fresh moments         (groupnorm.py:46-48)
