@@ -5,24 +5,30 @@
 // slot: the own strip's fresh K/V and the peers' stale K/V are never
 // concatenated.  The same kernel serves cross-attention (one slot, 77 tokens).
 //
-// One CTA = 128 queries of one (image, head).  192 threads:
-//   warp 0      TMA producer: Q once, then a ring of {K tile, V tile} (128 tokens x 64)
-//   warp 1      tensor memory owner and tcgen05.mma issuer:
-//                 S[j&1]  = Q K_j^T        (128x128, K-major operands)
-//                 Opart[j&1] = P_j V_j     (128x64, V consumed MN-major as stored)
-//   warps 2..5  softmax: thread r owns query row r (= TMEM lane r): running max
-//               and sum, P_j -> fp16 -> swizzled shared memory, and the fp32
-//               output accumulator O (64 registers), rescaled on the fly.
-// S is double-buffered so Q K_{j+1}^T overlaps the softmax of tile j.
+// One CTA = 256 queries (two tiles of 128) of one (image, head).  320 threads:
+//   warp 0      TMA producer: both Q tiles once, then a ring of {K tile, V tile}
+//               (128 tokens x 64), shared by the two query tiles
+//   warp 1      tensor memory owner and tcgen05.mma issuer, alternating between
+//               the two query tiles g = 0, 1:
+//                 S_g     = Q_g K_j^T      (128x128, K-major operands)
+//                 Opart_g = P_g V_j        (128x64, V consumed MN-major as stored)
+//   warps 2..5  softmax group 0, warps 6..9 softmax group 1: thread r owns query
+//               row r of its tile (= TMEM lane r): running max and sum,
+//               P -> fp16 -> swizzled shared memory, and the fp32 output
+//               accumulator (64 registers), rescaled on the fly.
+// While one group runs its softmax the tensor core works for the other one.
 //
 // Roofline: tensor cores; algorithmic FLOPs = 4 * L_q * L_kv * 64 per (image, head).
+// With head dimension 64 the exponentials (one per score) cost as many issue
+// slots as the tensor core needs cycles, so ~50 % of tensor peak is the ceiling of
+// this formulation.
 #include "bxl_common.cuh"
 #include "bxl_host.h"
 #include "../../include/basedxl_b200.h"
 
 namespace bxl {
 
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 320;
 constexpr int kHeadDim = 64;
 constexpr int kTileQ = 128;
 constexpr int kTileKV = 128;
@@ -43,37 +49,45 @@ struct alignas(64) AttnParams {
 };
 
 struct AttnSmem {
-  static constexpr int kQ = 0;                               // 16 KB
-  static constexpr int kK = 16384;                           // kKvStages x 16 KB
+  static constexpr int kQ = 0;                               // 2 x 16 KB
+  static constexpr int kK = 32768;                           // kKvStages x 16 KB
   static constexpr int kV = kK + kKvStages * 16384;          // kKvStages x 16 KB
-  static constexpr int kP = kV + kKvStages * 16384;          // 2 x 16 KB (two 64-column halves)
-  static constexpr int kBar = kP + 32768;
+  static constexpr int kP = kV + kKvStages * 16384;          // 2 groups x 2 halves x 16 KB
+  static constexpr int kBar = kP + 65536;
   static constexpr int kTotal = kBar + 1024 + 1024;
 };
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t bar_base = smem_base + AttnSmem::kBar;
-  // barriers: q_full, kv_full[3], kv_empty[3], s_full[2], o_full[2], p_full
+  // barriers: q_full, kv_full[3], kv_empty[3], s_full[2], o_full[2], p_full[2]
   const uint32_t q_full = bar_base;
   auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bar_base + 8u * (1 + kKvStages + s); };
-  auto s_full = [&](int b) { return bar_base + 8u * (1 + 2 * kKvStages + b); };
-  auto o_full = [&](int b) { return bar_base + 8u * (3 + 2 * kKvStages + b); };
-  const uint32_t p_full = bar_base + 8u * (5 + 2 * kKvStages);
+  auto s_full = [&](int g) { return bar_base + 8u * (1 + 2 * kKvStages + g); };
+  auto o_full = [&](int g) { return bar_base + 8u * (3 + 2 * kKvStages + g); };
+  auto p_full = [&](int g) { return bar_base + 8u * (5 + 2 * kKvStages + g); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + AttnSmem::kBar + 512);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + AttnSmem::kBar + 520);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  constexpr uint32_t kTmemCols = 512;  // S0 [0,128) S1 [128,256) O0 [256,320) O1 [320,384)
+  constexpr uint32_t kTmemCols = 512;  // S_0 [0,128) S_1 [128,256) O_0 [256,320) O_1 [320,384)
 
-  const int q_tiles = (p.L_q + kTileQ - 1) / kTileQ;
-  const int qt = blockIdx.x % q_tiles;
-  const int head = (blockIdx.x / q_tiles) % p.heads;
-  const int img = blockIdx.x / (q_tiles * p.heads);
+  const int q_pairs = (p.L_q + 2 * kTileQ - 1) / (2 * kTileQ);
+  const int qp = blockIdx.x % q_pairs;
+  const int head = (blockIdx.x / q_pairs) % p.heads;
+  const int img = blockIdx.x / (q_pairs * p.heads);
+  const int q_row0 = qp * 2 * kTileQ;
+  const int n_groups = (q_row0 + kTileQ < p.L_q) ? 2 : 1;   // the second tile may lie wholly past L_q
   const int tiles_per_slot = (p.L_slot + kTileKV - 1) / kTileKV;
   const int n_tiles = p.n_slots * tiles_per_slot;
 
@@ -83,11 +97,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
       mbar_init(kv_full(s), 1);
       mbar_init(kv_empty(s), 1);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(s_full(b), 1);
-      mbar_init(o_full(b), 1);
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(s_full(g), 1);
+      mbar_init(o_full(g), 1);
+      mbar_init(p_full(g), 128);
     }
-    mbar_init(p_full, 128);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -104,8 +118,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
     // ======================= TMA producer =======================
     if (lane == 0) {
       tma_prefetch_desc(&p.q_map);
-      mbar_arrive_expect_tx(q_full, 16384);
-      tma_load_3d(smem_base + AttnSmem::kQ, &p.q_map, q_full, head * kHeadDim, qt * kTileQ, img);
+      mbar_arrive_expect_tx(q_full, 16384u * n_groups);
+      for (int g = 0; g < n_groups; ++g)
+        tma_load_3d(smem_base + AttnSmem::kQ + g * 16384, &p.q_map, q_full, head * kHeadDim, q_row0 + g * kTileQ, img);
       int stage = 0;
       uint32_t phase = 0;
       for (int j = 0; j < n_tiles; ++j) {
@@ -127,159 +142,180 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_f16(128, 128, 0, 0);  // S = Q K^T, both K-major
       const uint32_t idesc_o = make_idesc_f16(128, 64, 0, 1);   // O = P V, V MN-major
-      const uint64_t qdesc = make_smem_desc_sw128(smem_base + AttnSmem::kQ, 16, 1024);
-      const uint64_t pdesc0 = make_smem_desc_sw128(smem_base + AttnSmem::kP, 16, 1024);
-      const uint64_t pdesc1 = make_smem_desc_sw128(smem_base + AttnSmem::kP + 16384, 16, 1024);
       bool ok = mbar_wait(q_full, 0, abort_flag, p.dev_status, 500);
-      auto issue_s = [&](int j) -> bool {
+      auto issue_s = [&](int j, int g) {
         const int st = j % kKvStages;
-        const uint32_t ph = (j / kKvStages) & 1u;
-        if (!mbar_wait(kv_full(st), ph, abort_flag, p.dev_status, 501)) return false;
-        tc_fence_after_sync();
+        const uint64_t qdesc = make_smem_desc_sw128(smem_base + AttnSmem::kQ + g * 16384, 16, 1024);
         const uint64_t kdesc = make_smem_desc_sw128(smem_base + AttnSmem::kK + st * 16384, 16, 1024);
-        const uint32_t d = tmem_base + (j & 1) * 128;
+        const uint32_t d = tmem_base + g * 128;
 #pragma unroll
         for (int k = 0; k < kHeadDim / 16; ++k) umma_f16(d, qdesc + 2u * k, kdesc + 2u * k, idesc_s, k != 0);
-        umma_commit(s_full(j & 1));
+        umma_commit(s_full(g));
+      };
+      auto wait_kv = [&](int j) -> bool {
+        if (!mbar_wait(kv_full(j % kKvStages), (j / kKvStages) & 1u, abort_flag, p.dev_status, 501)) return false;
+        tc_fence_after_sync();
         return true;
       };
-      if (ok && n_tiles > 0) ok = issue_s(0);
+      if (ok && n_tiles > 0) {
+        ok = wait_kv(0);
+        if (ok)
+          for (int g = 0; g < n_groups; ++g) issue_s(0, g);
+      }
       for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles) {
-          if (!issue_s(j + 1)) break;
-        }
-        // P_j is in shared memory once all 128 softmax threads have arrived
-        if (!mbar_wait(p_full, j & 1u, abort_flag, p.dev_status, 502)) break;
-        tc_fence_after_sync();
         const int st = j % kKvStages;
         // V tile [128 tokens][64] as stored: MN-major B operand, 8-token groups 1 KB apart
         const uint64_t vdesc = make_smem_desc_sw128(smem_base + AttnSmem::kV + st * 16384, 16, 1024);
-        const uint32_t d = tmem_base + 256 + (j & 1) * 64;
+        if (j + 1 < n_tiles && !wait_kv(j + 1)) break;
+        for (int g = 0; g < n_groups && ok; ++g) {
+          // P_g(j) is in shared memory, S_g and Opart_g are free again
+          if (!mbar_wait(p_full(g), j & 1u, abort_flag, p.dev_status, 502)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint64_t pdesc0 = make_smem_desc_sw128(smem_base + AttnSmem::kP + g * 32768, 16, 1024);
+          const uint64_t pdesc1 = make_smem_desc_sw128(smem_base + AttnSmem::kP + g * 32768 + 16384, 16, 1024);
+          const uint32_t d = tmem_base + 256 + g * 64;
 #pragma unroll
-        for (int k = 0; k < kTileKV / 16; ++k) {
-          // tokens 16k..16k+15: P columns are K-major (32 B per step inside a 64-column half),
-          // V rows advance by 16 x 128 B
-          const uint64_t pd = ((k < 4) ? pdesc0 : pdesc1) + 2u * (k & 3);
-          umma_f16(d, pd, vdesc + 128u * k, idesc_o, k != 0);
+          for (int k = 0; k < kTileKV / 16; ++k) {
+            // tokens 16k..16k+15: P columns are K-major (32 B per step inside a 64-column half),
+            // V rows advance by 16 x 128 B
+            const uint64_t pd = ((k < 4) ? pdesc0 : pdesc1) + 2u * (k & 3);
+            umma_f16(d, pd, vdesc + 128u * k, idesc_o, k != 0);
+          }
+          umma_commit(o_full(g));
+          if (g == n_groups - 1) umma_commit(kv_empty(st));  // K_j and V_j are no longer needed
+          if (j + 1 < n_tiles) issue_s(j + 1, g);
         }
-        umma_commit(kv_empty(st));
-        umma_commit(o_full(j & 1));
       }
     }
   } else {
-    // ======================= softmax / output (warps 2..5) =======================
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;  // query row inside the tile == TMEM lane
-    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    float o_acc[kHeadDim];
+    // ======================= softmax / output (warps 2..9) =======================
+    const int g = (warp - 2) >> 2;         // query tile served by this warp
+    const int quarter = warp & 3;          // TMEM lane quarter this warp may access
+    const int row = quarter * 32 + lane;   // query row inside the tile == TMEM lane
+    if (g < n_groups) {
+      const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      const uint32_t s_addr = t_lane + g * 128;
+      const uint32_t o_addr = t_lane + 256 + g * 64;
+      float o_acc[kHeadDim];
 #pragma unroll
-    for (int i = 0; i < kHeadDim; ++i) o_acc[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
-    uint8_t* p_smem = smem_gen + AttnSmem::kP;
-    bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int t0 = (j % tiles_per_slot) * kTileKV;
-      const int valid = min(kTileKV, p.L_slot - t0);
-      if (!mbar_wait(s_full(j & 1), (j >> 1) & 1u, abort_flag, p.dev_status, 600)) {
-        ok = false;
-        break;
-      }
-      __syncwarp();
-      tc_fence_after_sync();
-      const uint32_t s_addr = t_lane + (j & 1) * 128;
-      // pass 1: row maximum
-      float m_tile = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(s_addr + c * 32, v);
+      for (int i = 0; i < kHeadDim; ++i) o_acc[i] = 0.f;
+      float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+      uint8_t* p_smem = smem_gen + AttnSmem::kP + g * 32768;
+      const float sc = p.scale_log2e;
+      bool ok = true;
+      auto add_opart = [&]() {
+        uint32_t v0[32], v1[32];
+        tmem_ld_32x32(o_addr, v0);
+        tmem_ld_32x32(o_addr + 32, v1);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (c * 32 + i < valid) m_tile = fmaxf(m_tile, __uint_as_float(v[i]));
-      }
-      const float m_new = fmaxf(m_run, m_tile * p.scale_log2e);
-      const float alpha = exp2f(m_run - m_new);  // exp2f(-inf) = 0 on the first tile
-      // the previous tile's P V product: frees the P buffer and delivers Opart_{j-1}
-      if (j > 0) {
-        if (!mbar_wait(o_full((j - 1) & 1), ((j - 1) >> 1) & 1u, abort_flag, p.dev_status, 601)) {
+        for (int i = 0; i < 32; ++i) {
+          o_acc[i] = o_acc[i] * alpha_prev + __uint_as_float(v0[i]);
+          o_acc[32 + i] = o_acc[32 + i] * alpha_prev + __uint_as_float(v1[i]);
+        }
+      };
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int t0 = (j % tiles_per_slot) * kTileKV;
+        const int valid = min(kTileKV, p.L_slot - t0);
+        if (!mbar_wait(s_full(g), j & 1u, abort_flag, p.dev_status, 600)) {
           ok = false;
           break;
         }
         __syncwarp();
         tc_fence_after_sync();
-        const uint32_t o_addr = t_lane + 256 + ((j - 1) & 1) * 64;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(o_addr + c * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha_prev + __uint_as_float(v[i]);
-        }
-      }
-      // pass 2: P = exp2(S*scale - m), row sum, fp16 into swizzled shared memory
-      float l_tile = 0.f;
+        // pass 1: row maximum
+        float m_tile = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(s_addr + c * 32, v);
-        tmem_ld_wait();
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int col = c * 32 + 2 * i;
-          float p0 = (col < valid) ? exp2f(__uint_as_float(v[2 * i]) * p.scale_log2e - m_new) : 0.f;
-          float p1 = (col + 1 < valid) ? exp2f(__uint_as_float(v[2 * i + 1]) * p.scale_log2e - m_new) : 0.f;
-          const __half2 h = __floats2half2_rn(p0, p1);
-          // the row sum uses the rounded values the tensor core will see
-          const float2 hr = __half22float2(h);
-          l_tile += hr.x + hr.y;
-          packed[i] = *reinterpret_cast<const uint32_t*>(&h);
-        }
-        // 32 columns = 4 chunks of 16 B; half = c/2, chunk index inside the half = (c%2)*4 + q
-        uint8_t* half_base = p_smem + (c >> 1) * 16384;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint32_t off = sw128_offset(row, (c & 1) * 4 + q);
-          *reinterpret_cast<uint4*>(half_base + off) =
-              make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-        }
-      }
-      l_run = l_run * alpha + l_tile;
-      m_run = m_new;
-      alpha_prev = alpha;
-      // publish P_j (generic-proxy writes -> async proxy) and release S[j&1]
-      fence_proxy_async_smem();
-      tc_fence_before_sync();
-      mbar_arrive(p_full);
-    }
-    if (ok && n_tiles > 0) {
-      const int j = n_tiles - 1;
-      if (mbar_wait(o_full(j & 1), (j >> 1) & 1u, abort_flag, p.dev_status, 602)) {
-        __syncwarp();
-        tc_fence_after_sync();
-        const uint32_t o_addr = t_lane + 256 + (j & 1) * 64;
-#pragma unroll
         for (int c = 0; c < 2; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(o_addr + c * 32, v);
+          uint32_t v0[32], v1[32];
+          tmem_ld_32x32(s_addr + c * 64, v0);
+          tmem_ld_32x32(s_addr + c * 64 + 32, v1);
           tmem_ld_wait();
+          if (valid == kTileKV) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha_prev + __uint_as_float(v[i]);
+            for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, fmaxf(__uint_as_float(v0[i]), __uint_as_float(v1[i])));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (c * 64 + i < valid) m_tile = fmaxf(m_tile, __uint_as_float(v0[i]));
+              if (c * 64 + 32 + i < valid) m_tile = fmaxf(m_tile, __uint_as_float(v1[i]));
+            }
+          }
         }
-        const int q_row = qt * kTileQ + row;
-        if (q_row < p.L_q) {
-          const float inv_l = 1.f / l_run;
-          __half* dst = p.out + (long long)img * p.out_img_stride + (long long)q_row * p.ld_out + head * kHeadDim;
+        const float m_new = fmaxf(m_run, m_tile * sc);
+        const float alpha = fast_exp2(m_run - m_new);  // 0 on the first tile (m_run = -inf)
+        // the previous tile's P V product: frees the P buffer and delivers Opart(j-1)
+        if (j > 0) {
+          if (!mbar_wait(o_full(g), (j - 1) & 1u, abort_flag, p.dev_status, 601)) {
+            ok = false;
+            break;
+          }
+          __syncwarp();
+          tc_fence_after_sync();
+          add_opart();
+        }
+        // pass 2: P = exp2(S*scale - m), row sum, fp16 into swizzled shared memory
+        float l_tile = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(s_addr + c * 32, v);
+          tmem_ld_wait();
+          uint32_t packed[16];
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            uint4 u;
-            __half2* h = reinterpret_cast<__half2*>(&u);
+          for (int i = 0; i < 16; ++i) {
+            float p0 = fast_exp2(fmaf(__uint_as_float(v[2 * i]), sc, -m_new));
+            float p1 = fast_exp2(fmaf(__uint_as_float(v[2 * i + 1]), sc, -m_new));
+            if (valid != kTileKV) {
+              const int col = c * 32 + 2 * i;
+              if (col >= valid) p0 = 0.f;
+              if (col + 1 >= valid) p1 = 0.f;
+            }
+            const __half2 h = __floats2half2_rn(p0, p1);
+            // the row sum uses the rounded values the tensor core will see
+            const float2 hr = __half22float2(h);
+            l_tile += hr.x + hr.y;
+            packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+          }
+          // 32 columns = 4 chunks of 16 B; half = c/2, chunk index inside the half = (c%2)*4 + q
+          uint8_t* half_base = p_smem + (c >> 1) * 16384;
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              h[i] = __floats2half2_rn(o_acc[q * 8 + 2 * i] * inv_l, o_acc[q * 8 + 2 * i + 1] * inv_l);
-            *reinterpret_cast<uint4*>(dst + q * 8) = u;
+          for (int q = 0; q < 4; ++q) {
+            const uint32_t off = sw128_offset(row, (c & 1) * 4 + q);
+            *reinterpret_cast<uint4*>(half_base + off) =
+                make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+          }
+        }
+        l_run = l_run * alpha + l_tile;
+        m_run = m_new;
+        alpha_prev = alpha;
+        // publish P(j) (generic-proxy writes -> async proxy); S_g and Opart_g are free
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        mbar_arrive(p_full(g));
+      }
+      if (ok && n_tiles > 0) {
+        const int j = n_tiles - 1;
+        if (mbar_wait(o_full(g), j & 1u, abort_flag, p.dev_status, 602)) {
+          __syncwarp();
+          tc_fence_after_sync();
+          add_opart();
+          const int q_row = q_row0 + g * kTileQ + row;
+          if (q_row < p.L_q) {
+            const float inv_l = 1.f / l_run;
+            __half* dst = p.out + (long long)img * p.out_img_stride + (long long)q_row * p.ld_out + head * kHeadDim;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              uint4 u;
+              __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                h[i] = __floats2half2_rn(o_acc[q * 8 + 2 * i] * inv_l, o_acc[q * 8 + 2 * i + 1] * inv_l);
+              *reinterpret_cast<uint4*>(dst + q * 8) = u;
+            }
           }
         }
       }
@@ -350,7 +386,7 @@ extern "C" int bxl_attn_fwd_f16(const void* q, long long q_img_stride, long long
       return rc;
     configured[dev] = true;
   }
-  const int q_tiles = (L_q + kTileQ - 1) / kTileQ;
-  attention_kernel<<<q_tiles * heads * B, kAttnThreads, AttnSmem::kTotal, (cudaStream_t)stream>>>(p);
+  const int q_pairs = (L_q + 2 * kTileQ - 1) / (2 * kTileQ);
+  attention_kernel<<<q_pairs * heads * B, kAttnThreads, AttnSmem::kTotal, (cudaStream_t)stream>>>(p);
   return check_cuda(cudaGetLastError(), "attention_kernel launch");
 }
