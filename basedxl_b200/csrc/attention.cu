@@ -15,7 +15,10 @@
 //   warps 2..5  softmax group 0, warps 6..9 softmax group 1: thread r owns query
 //               row r of its tile (= TMEM lane r): running max and sum,
 //               P -> fp16 -> swizzled shared memory, and the fp32 output
-//               accumulator (64 registers), rescaled on the fly.
+//               accumulator (64 registers), rescaled on the fly.  Exponentials are
+//               taken two per MUFU operation (ex2 on packed fp16, argument formed in
+//               fp32); the row sums of the rounded P come from a 16-column product
+//               with a matrix of ones on the tensor core.
 // While one group runs its softmax the tensor core works for the other one.
 //
 // Roofline: tensor cores; algorithmic FLOPs = 4 * L_q * L_kv * 64 per (image, head).
@@ -53,7 +56,8 @@ struct AttnSmem {
   static constexpr int kK = 32768;                           // kKvStages x 16 KB
   static constexpr int kV = kK + kKvStages * 16384;          // kKvStages x 16 KB
   static constexpr int kP = kV + kKvStages * 16384;          // 2 groups x 2 halves x 16 KB
-  static constexpr int kBar = kP + 65536;
+  static constexpr int kOnes = kP + 65536;                   // 16 rows x 128 fp16 of 1.0 (two 2 KB halves): row-sum operand
+  static constexpr int kBar = kOnes + 4096;
   static constexpr int kTotal = kBar + 1024 + 1024;
 };
 
@@ -61,6 +65,23 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// two exponentials per MUFU operation: exp2 of a packed pair of fp16 arguments
+__device__ __forceinline__ uint32_t exp2_f16x2(float a, float b) {
+  uint32_t packed, y;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(b), "f"(a));  // low half = a, high half = b
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(packed));
+  return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ uint32_t tmem_ld_1(uint32_t taddr) {
+  uint32_t r;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
+  return r;
 }
 
 __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid_constant__ AttnParams p) {
@@ -80,7 +101,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  constexpr uint32_t kTmemCols = 512;  // S_0 [0,128) S_1 [128,256) O_0 [256,320) O_1 [320,384)
+  // S_0 [0,128) S_1 [128,256) O_0 [256,320) O_1 [320,384) L_0 [384,400) L_1 [400,416)
+  constexpr uint32_t kTmemCols = 512;
 
   const int q_pairs = (p.L_q + 2 * kTileQ - 1) / (2 * kTileQ);
   const int qp = blockIdx.x % q_pairs;
@@ -109,6 +131,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
     tmem_relinquish();
   }
+  // constant operand of the row-sum product: every element 1.0 (layout-agnostic)
+  for (int i = threadIdx.x; i < 4096 / 4; i += blockDim.x)
+    reinterpret_cast<uint32_t*>(smem_gen + AttnSmem::kOnes)[i] = 0x3C003C00u;
+  fence_proxy_async_smem();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -142,6 +168,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_f16(128, 128, 0, 0);  // S = Q K^T, both K-major
       const uint32_t idesc_o = make_idesc_f16(128, 64, 0, 1);   // O = P V, V MN-major
+      const uint32_t idesc_l = make_idesc_f16(128, 16, 0, 0);   // row sums: L = P 1 (16 identical columns)
+      const uint64_t ones0 = make_smem_desc_sw128(smem_base + AttnSmem::kOnes, 16, 1024);
+      const uint64_t ones1 = make_smem_desc_sw128(smem_base + AttnSmem::kOnes + 2048, 16, 1024);
       bool ok = mbar_wait(q_full, 0, abort_flag, p.dev_status, 500);
       auto issue_s = [&](int j, int g) {
         const int st = j % kKvStages;
@@ -184,6 +213,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
             const uint64_t pd = ((k < 4) ? pdesc0 : pdesc1) + 2u * (k & 3);
             umma_f16(d, pd, vdesc + 128u * k, idesc_o, k != 0);
           }
+          // row sums of the rounded P on the tensor core, exact in fp32
+          const uint32_t dl = tmem_base + 384 + g * 16;
+#pragma unroll
+          for (int k = 0; k < kTileKV / 16; ++k) {
+            const uint64_t pd = ((k < 4) ? pdesc0 : pdesc1) + 2u * (k & 3);
+            umma_f16(dl, pd, ((k < 4) ? ones0 : ones1) + 2u * (k & 3), idesc_l, k != 0);
+          }
           umma_commit(o_full(g));
           if (g == n_groups - 1) umma_commit(kv_empty(st));  // K_j and V_j are no longer needed
           if (j + 1 < n_tiles) issue_s(j + 1, g);
@@ -206,16 +242,20 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
       uint8_t* p_smem = smem_gen + AttnSmem::kP + g * 32768;
       const float sc = p.scale_log2e;
       bool ok = true;
+      const uint32_t l_addr = t_lane + 384 + g * 16;
+      // O = O*alpha + Opart, l = l*alpha + Lpart for the tile whose P V product just finished
       auto add_opart = [&]() {
         uint32_t v0[32], v1[32];
         tmem_ld_32x32(o_addr, v0);
         tmem_ld_32x32(o_addr + 32, v1);
+        const uint32_t lp = tmem_ld_1(l_addr);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          o_acc[i] = o_acc[i] * alpha_prev + __uint_as_float(v0[i]);
-          o_acc[32 + i] = o_acc[32 + i] * alpha_prev + __uint_as_float(v1[i]);
+          o_acc[i] = fmaf(o_acc[i], alpha_prev, __uint_as_float(v0[i]));
+          o_acc[32 + i] = fmaf(o_acc[32 + i], alpha_prev, __uint_as_float(v1[i]));
         }
+        l_run = fmaf(l_run, alpha_prev, __uint_as_float(lp));
       };
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int t0 = (j % tiles_per_slot) * kTileKV;
@@ -236,7 +276,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
           tmem_ld_wait();
           if (valid == kTileKV) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, fmaxf(__uint_as_float(v0[i]), __uint_as_float(v1[i])));
+            for (int i = 0; i < 32; ++i) m_tile = max3(m_tile, __uint_as_float(v0[i]), __uint_as_float(v1[i]));
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
@@ -247,7 +287,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
         }
         const float m_new = fmaxf(m_run, m_tile * sc);
         const float alpha = fast_exp2(m_run - m_new);  // 0 on the first tile (m_run = -inf)
-        // the previous tile's P V product: frees the P buffer and delivers Opart(j-1)
+        // the previous tile's P V product: frees the P buffer and delivers Opart(j-1), Lpart(j-1)
         if (j > 0) {
           if (!mbar_wait(o_full(g), (j - 1) & 1u, abort_flag, p.dev_status, 601)) {
             ok = false;
@@ -257,42 +297,39 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
           tc_fence_after_sync();
           add_opart();
         }
-        // pass 2: P = exp2(S*scale - m), row sum, fp16 into swizzled shared memory
-        float l_tile = 0.f;
+        // pass 2: P = exp2(S*scale - m) as fp16 into swizzled shared memory (the row sum is
+        // taken by the tensor core from the same rounded values)
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(s_addr + c * 32, v);
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v0[32], v1[32];
+          tmem_ld_32x32(s_addr + c * 64, v0);
+          tmem_ld_32x32(s_addr + c * 64 + 32, v1);
           tmem_ld_wait();
-          uint32_t packed[16];
+          uint32_t packed[32];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            float p0 = fast_exp2(fmaf(__uint_as_float(v[2 * i]), sc, -m_new));
-            float p1 = fast_exp2(fmaf(__uint_as_float(v[2 * i + 1]), sc, -m_new));
-            if (valid != kTileKV) {
-              const int col = c * 32 + 2 * i;
-              if (col >= valid) p0 = 0.f;
-              if (col + 1 >= valid) p1 = 0.f;
-            }
-            const __half2 h = __floats2half2_rn(p0, p1);
-            // the row sum uses the rounded values the tensor core will see
-            const float2 hr = __half22float2(h);
-            l_tile += hr.x + hr.y;
-            packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+            packed[i] = exp2_f16x2(fmaf(__uint_as_float(v0[2 * i]), sc, -m_new), fmaf(__uint_as_float(v0[2 * i + 1]), sc, -m_new));
+            packed[16 + i] = exp2_f16x2(fmaf(__uint_as_float(v1[2 * i]), sc, -m_new), fmaf(__uint_as_float(v1[2 * i + 1]), sc, -m_new));
           }
-          // 32 columns = 4 chunks of 16 B; half = c/2, chunk index inside the half = (c%2)*4 + q
-          uint8_t* half_base = p_smem + (c >> 1) * 16384;
+          if (valid != kTileKV) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const uint32_t off = sw128_offset(row, (c & 1) * 4 + q);
-            *reinterpret_cast<uint4*>(half_base + off) =
+            for (int i = 0; i < 32; ++i) {
+              const int col = c * 64 + 2 * i;
+              if (col >= valid) packed[i] = 0u;
+              else if (col + 1 >= valid) packed[i] &= 0x0000FFFFu;
+            }
+          }
+          // 64 columns = one 64-column half of the P tile: 8 chunks of 16 B
+          uint8_t* half_base = p_smem + c * 16384;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            *reinterpret_cast<uint4*>(half_base + sw128_offset(row, q)) =
                 make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
           }
         }
-        l_run = l_run * alpha + l_tile;
         m_run = m_new;
         alpha_prev = alpha;
-        // publish P(j) (generic-proxy writes -> async proxy); S_g and Opart_g are free
+        // publish P(j) (generic-proxy writes -> async proxy); S_g, Opart_g and Lpart_g are free
         fence_proxy_async_smem();
         tc_fence_before_sync();
         mbar_arrive(p_full(g));
