@@ -76,8 +76,12 @@ class BasedXLCrossAttentionPP(BasedXLAttentionPP):
         attn = self.module
         recompute_kv = self.counter == 0
         q = _lin(attn.to_q, hidden_states)
-        if recompute_kv or self.kv_cache is None:
+        b, l, _ = encoder_hidden_states.shape
+        if self.kv_cache is None or self.kv_cache.shape[:2] != (b, l):
             self.kv_cache = _lin(self.to_kv, encoder_hidden_states)
+        elif recompute_kv:
+            # refresh in place: a captured step graph keeps reading this storage
+            _lin(self.to_kv, encoder_hidden_states, out=self.kv_cache.view(b * l, -1))
         o = ops.attention(q, [self.kv_cache], attn.heads)
         y = _finish(attn, o, hidden_states, residual)
         self.counter += 1

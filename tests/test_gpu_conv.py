@@ -190,3 +190,30 @@ def test_conv_forced_tile_width_and_k_split(bn, split):
             assert_close(y, ref, what=f"conv bn={bn} split={split} strip {i}")
     finally:
         _lib.check(l.bxl_debug_force_tiles(0, 0), l, kernels=0)
+
+
+@pytest.mark.parametrize("n", [1, 2, 4, 8])
+def test_auto_tiling_on_every_per_rank_conv_shape(n):
+    """The 3x3 convolutions of the UNet on the strips a rank sees when the image is split
+    n ways (batch 1), with the tiling the library chooses by itself, against cuDNN fp32."""
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(n)
+    sites = [(320, 320, 128, 1), (320, 320, 128, 2), (640, 640, 64, 1), (640, 640, 64, 2), (1280, 1280, 32, 1), (2560, 1280, 32, 1),
+             (1920, 1280, 32, 1), (1280, 1280, 64, 1), (1920, 640, 64, 1), (960, 640, 64, 1), (640, 640, 128, 1), (960, 320, 128, 1),
+             (640, 320, 128, 1), (320, 640, 64, 1), (640, 1280, 32, 1)]
+    for (ci, co, hw, stride) in sites:
+        hl = hw // n
+        if hl < stride or hl % stride:
+            continue
+        x = torch.randn(1, hl, hw, ci, device=dev, generator=g).half()
+        top = torch.randn(1, 1, hw, ci, device=dev, generator=g).half()
+        bot = torch.randn(1, 1, hw, ci, device=dev, generator=g).half()
+        w = (torch.randn(co, ci, 3, 3, device=dev, generator=g) / (9 * ci) ** 0.5).half()
+        b = torch.randn(co, device=dev, generator=g).half()
+        y = ops.conv3x3(x, ops.conv_weight_pack(w), b, stride=stride, top=top, bot=bot)
+        padded = torch.cat([top, x, bot], dim=1).permute(0, 3, 1, 2).float()
+        ref = torch.nn.functional.conv2d(padded, w.float(), b.float(), stride=stride, padding=(0, 1)).permute(0, 2, 3, 1)
+        err = float((y.float() - ref).norm() / ref.norm())
+        assert torch.isfinite(y).all() and err < 2e-3, f"n={n} {ci}->{co} @{hw} s{stride}: rel-L2 {err:.3e}"
+    _lib.device_status()

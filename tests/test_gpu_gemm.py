@@ -132,3 +132,23 @@ def test_forced_tile_width_and_k_split(M, K, N, b_is_kn, bn, split):
     finally:
         _lib.check(l.bxl_debug_force_tiles(0, 0), l, kernels=0)
     assert_close(y, ref, what=f"gemm bn={bn} split={split}")
+
+
+@pytest.mark.parametrize("tokens", [8192, 4096, 2048, 1024, 512, 256])
+def test_auto_tiling_on_every_per_rank_linear_shape(tokens):
+    """The linear-layer shapes of the UNet at the token counts a rank sees with 1, 2, 4
+    or 8 GPUs, each with the tiling the library chooses by itself (tile width, K split),
+    against an fp32 matmul on the device."""
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(tokens)
+    for (K, N) in [(640, 640), (640, 1280), (640, 5120), (2560, 640), (1280, 1280), (1280, 2560), (1280, 10240), (5120, 1280),
+                   (2048, 1280), (2048, 2560), (320, 1280), (2816, 1280)]:
+        a = torch.randn(tokens, K, device=dev, generator=g).half()
+        w = (torch.randn(N, K, device=dev, generator=g) / K**0.5).half()
+        bias = torch.randn(N, device=dev, generator=g).half()
+        y = ops.gemm(a, w, bias=bias)
+        ref = a.float() @ w.float().t() + bias.float()
+        err = float((y.float() - ref).norm() / ref.norm())
+        assert torch.isfinite(y).all() and err < 2e-3, f"tokens={tokens} K={K} N={N}: rel-L2 {err:.3e}"
+    _lib.device_status()

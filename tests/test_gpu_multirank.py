@@ -57,7 +57,12 @@ def _worker(rank, world, use_cfg, graph, port, ret):
         return o
 
     pipe.unet.forward = spy
-    final = pipe.denoise(T("in_latents").float(), T("in_ehs").half(), added, TOTAL_STEPS, GUIDANCE, first_step=0, last_step=STEPS)
+    # two images in a row: the second one re-enters the synchronous phase and then replays
+    # whatever the first one captured, so everything a graph reads must have stayed in place
+    for image in range(2):
+        outs.clear()
+        pipe.unet.reset()
+        final = pipe.denoise(T("in_latents").float(), T("in_ehs").half(), added, TOTAL_STEPS, GUIDANCE, first_step=0, last_step=STEPS)
     pipe.unet.comm_manager.clear()
     torch.cuda.synchronize()
     _lib.device_status()
