@@ -99,6 +99,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + AttnSmem::kBar + 512);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + AttnSmem::kBar + 520);
 
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   // S_0 [0,128) S_1 [128,256) O_0 [256,320) O_1 [320,384) L_0 [384,400) L_1 [400,416)
@@ -139,6 +140,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();  // the set-up above overlaps the previous kernel's tail; global data from here on
 
   if (warp == 0) {
     // ======================= TMA producer =======================
@@ -424,6 +426,6 @@ extern "C" int bxl_attn_fwd_f16(const void* q, long long q_img_stride, long long
     configured[dev] = true;
   }
   const int q_pairs = (L_q + 2 * kTileQ - 1) / (2 * kTileQ);
-  attention_kernel<<<q_pairs * heads * B, kAttnThreads, AttnSmem::kTotal, (cudaStream_t)stream>>>(p);
-  return check_cuda(cudaGetLastError(), "attention_kernel launch");
+  return launch_kernel("attention_kernel launch", attention_kernel, dim3(q_pairs * heads * B), dim3(kAttnThreads),
+                       AttnSmem::kTotal, (cudaStream_t)stream, 1, p);
 }

@@ -150,6 +150,16 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
   }
 }
 
+// ---- programmatic dependent launch -----------------------------------------
+// Kernels are launched with programmatic stream serialisation: the next kernel in
+// the stream may begin its prologue (barrier set-up, tensor-memory allocation,
+// descriptor prefetch) while this one drains.  pdl_launch_dependents() lets the
+// successor start; pdl_wait() returns once every predecessor grid has completed and
+// its memory is visible, and must precede the first access to global data.
+// Both are no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- proxies / fences -------------------------------------------------------
 // Make generic-proxy writes to shared memory visible to the async proxy (TMA,
 // tcgen05.mma operand fetch).

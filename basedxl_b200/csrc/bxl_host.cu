@@ -2,6 +2,7 @@
 
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "../../include/basedxl_b200.h"
@@ -51,6 +52,15 @@ int sm_count() {
     g_sm_count[dev] = n;
   }
   return g_sm_count[dev];
+}
+
+static int g_pdl = -1;
+bool pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* e = getenv("BXL_PDL");
+    g_pdl = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_pdl != 0;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -125,5 +135,10 @@ int bxl_device_status(int* code, int* site, int* block) {
 }
 
 int bxl_sm_count(void) { return bxl::sm_count(); }
+
+int bxl_set_pdl(int enabled) {
+  bxl::g_pdl = enabled ? 1 : 0;
+  return bxl::kOk;
+}
 
 }  // extern "C"

@@ -29,4 +29,37 @@ int encode_tmap_f16(CUtensorMap* out, const void* base, int rank, const uint64_t
 
 int sm_count();
 
+// Whether kernels are launched with programmatic stream serialisation (default on;
+// BXL_PDL=0 in the environment or bxl_set_pdl(0) turns it off).
+bool pdl_enabled();
+
+// Launch through cudaLaunchKernelEx with the programmatic-serialisation attribute and
+// an optional thread-block cluster width.
+template <typename... KArgs, typename... Args>
+int launch_kernel(const char* what, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                  int cluster_x, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return check_cuda(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...), what);
+}
+
 }  // namespace bxl

@@ -13,6 +13,8 @@ namespace bxl {
 // ---- halo pack: first and last `pad` rows of a strip -> [2][B][pad][W][C] ----
 __global__ void halo_pack_kernel(const uint4* __restrict__ x, long long img_stride_v, uint4* __restrict__ out, int B, int H,
                                  long long row_v, int pad) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long per = (long long)pad * row_v;  // vectors per (side, image)
   const long long total = 2ll * B * per;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -31,6 +33,8 @@ __global__ void conv3x3_small_cin_kernel(const __half* __restrict__ x, long long
                                          const __half* __restrict__ bot, long long halo_img_stride,
                                          const __half* __restrict__ w, const __half* __restrict__ bias, __half* __restrict__ y,
                                          int B, int Cin, int Cout, int H, int W) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float s_w[];  // [9*Cin][Cout]: threads of a warp (consecutive output vectors) read consecutive words
   const int K = 9 * Cin;
   for (int i = threadIdx.x; i < Cout * K; i += blockDim.x) s_w[(i % K) * Cout + i / K] = __half2float(w[i]);
@@ -87,6 +91,8 @@ __global__ void conv3x3_small_cout_kernel(const __half* __restrict__ x, long lon
                                           const __half* __restrict__ bot, long long halo_img_stride,
                                           const __half* __restrict__ w, const __half* __restrict__ bias, __half* __restrict__ y,
                                           int B, int Cin, int H, int W) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int warps_per_block = blockDim.x / 32;
   const int lane = threadIdx.x & 31;
   const long long total = (long long)B * H * W;
@@ -146,6 +152,8 @@ __global__ void conv3x3_small_cout_kernel(const __half* __restrict__ x, long lon
 
 // ---- nearest-neighbour 2x up-sampling ---------------------------------------------
 __global__ void upsample2x_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int B, int H, int W, int vecs) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long total = (long long)B * (2 * H) * (2 * W) * vecs;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const int v = i % vecs;
@@ -160,6 +168,8 @@ __global__ void upsample2x_kernel(const uint4* __restrict__ x, uint4* __restrict
 // ---- LayerNorm over the last axis, one warp per row --------------------------------
 __global__ void layernorm_kernel(const __half* __restrict__ x, __half* __restrict__ y, const __half* __restrict__ gamma,
                                  const __half* __restrict__ beta, long long rows, int C, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x / 32;
   const int vecs = C / 8;
@@ -225,6 +235,8 @@ __global__ void layernorm_kernel(const __half* __restrict__ x, __half* __restric
 
 // ---- GEGLU: out[m, f] = h[m, f] * gelu(h[m, F + f]) ----------------------------------
 __global__ void geglu_kernel(const __half* __restrict__ h, __half* __restrict__ out, long long rows, int F) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int vecs = F / 8;
   const long long total = rows * vecs;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -267,9 +279,8 @@ extern "C" int bxl_halo_pack_f16(const void* x, long long img_stride, void* out,
   if (C % 8 || img_stride % 8 || !al16(x) || !al16(out)) return fail(kErrInvalidArg, "bxl_halo_pack_f16: C, stride and pointers must be 16-byte granular");
   const long long row_v = (long long)W * C / 8;
   const long long total = 2ll * B * pad * row_v;
-  halo_pack_kernel<<<grid_for(total, 256), 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4*>(x), img_stride / 8,
-                                                                           static_cast<uint4*>(out), B, H, row_v, pad);
-  return check_cuda(cudaGetLastError(), "halo_pack_kernel launch");
+  return launch_kernel("halo_pack_kernel launch", halo_pack_kernel, dim3(grid_for(total, 256)), dim3(256), 0, (cudaStream_t)stream, 1,
+                       static_cast<const uint4*>(x), img_stride / 8, static_cast<uint4*>(out), B, H, row_v, pad);
 }
 
 extern "C" int bxl_conv3x3_direct_f16(const void* x, long long x_img_stride, const void* top, const void* bot,
@@ -316,9 +327,8 @@ extern "C" int bxl_upsample2x_f16(const void* x, void* y, int B, int H, int W, i
   if (!x || !y || B <= 0 || H <= 0 || W <= 0 || C <= 0 || C % 8 || !al16(x) || !al16(y))
     return fail(kErrInvalidArg, "bxl_upsample2x_f16: bad argument");
   const long long total = (long long)B * 4 * H * W * (C / 8);
-  upsample2x_kernel<<<grid_for(total, 256), 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4*>(x),
-                                                                            static_cast<uint4*>(y), B, H, W, C / 8);
-  return check_cuda(cudaGetLastError(), "upsample2x_kernel launch");
+  return launch_kernel("upsample2x_kernel launch", upsample2x_kernel, dim3(grid_for(total, 256)), dim3(256), 0, (cudaStream_t)stream, 1,
+                       static_cast<const uint4*>(x), static_cast<uint4*>(y), B, H, W, C / 8);
 }
 
 extern "C" int bxl_layernorm_f16(const void* x, void* y, const void* gamma, const void* beta, long long rows, int C, float eps,
@@ -326,15 +336,13 @@ extern "C" int bxl_layernorm_f16(const void* x, void* y, const void* gamma, cons
   if (!x || !y || !gamma || !beta || rows <= 0 || C <= 0) return fail(kErrInvalidArg, "bxl_layernorm_f16: bad argument");
   if (C % 8 || C > 1536 || !al16(x) || !al16(y) || !al16(gamma) || !al16(beta))
     return fail(kErrUnsupported, "bxl_layernorm_f16: C=%d must be a multiple of 8, at most 1536, pointers 16-byte aligned", C);
-  layernorm_kernel<<<grid_for(rows * 32, 256), 256, 0, (cudaStream_t)stream>>>(
-      static_cast<const __half*>(x), static_cast<__half*>(y), static_cast<const __half*>(gamma),
-      static_cast<const __half*>(beta), rows, C, eps);
-  return check_cuda(cudaGetLastError(), "layernorm_kernel launch");
+  return launch_kernel("layernorm_kernel launch", layernorm_kernel, dim3(grid_for(rows * 32, 256)), dim3(256), 0, (cudaStream_t)stream, 1,
+                       static_cast<const __half*>(x), static_cast<__half*>(y), static_cast<const __half*>(gamma),
+                       static_cast<const __half*>(beta), rows, C, eps);
 }
 
 extern "C" int bxl_geglu_f16(const void* h, void* out, long long rows, int F, void* stream) {
   if (!h || !out || rows <= 0 || F <= 0 || F % 8 || !al16(h) || !al16(out)) return fail(kErrInvalidArg, "bxl_geglu_f16: bad argument");
-  geglu_kernel<<<grid_for(rows * (F / 8), 256), 256, 0, (cudaStream_t)stream>>>(static_cast<const __half*>(h),
-                                                                                  static_cast<__half*>(out), rows, F);
-  return check_cuda(cudaGetLastError(), "geglu_kernel launch");
+  return launch_kernel("geglu_kernel launch", geglu_kernel, dim3(grid_for(rows * (F / 8), 256)), dim3(256), 0, (cudaStream_t)stream, 1,
+                       static_cast<const __half*>(h), static_cast<__half*>(out), rows, F);
 }

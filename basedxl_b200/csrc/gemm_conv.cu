@@ -152,6 +152,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 8);
 
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t tmem_cols = (2 * BN <= 64) ? 64u : (2 * BN <= 128) ? 128u : (2 * BN <= 256) ? 256u : 512u;
@@ -181,6 +182,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
   if (S > 1) cluster_sync_all();  // peers' barriers are initialised before anyone arrives on them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();  // everything above overlaps the previous kernel's tail; global data from here on
 
   // ---- tile enumeration ------------------------------------------------------
   const int tiles_n = (p.N + BN - 1) / BN;
@@ -496,20 +498,8 @@ static int launch(const GemmParams& p, int num_tiles, cudaStream_t stream) {
   int clusters = sm_count() / p.split;
   if (clusters > num_tiles) clusters = num_tiles;
   if (clusters < 1) clusters = 1;
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(clusters * p.split);
-  cfg.blockDim = dim3(kGemmThreads);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = p.split;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = p.split > 1 ? 1 : 0;
-  return check_cuda(cudaLaunchKernelEx(&cfg, gemm_conv_kernel<kConv>, p), "gemm_conv_kernel launch");
+  return launch_kernel("gemm_conv_kernel launch", gemm_conv_kernel<kConv>, dim3(clusters * p.split), dim3(kGemmThreads), smem,
+                       stream, p.split, p);
 }
 
 static int aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -581,6 +571,8 @@ extern "C" int bxl_debug_force_tiles(int bn, int split) {
 namespace bxl {
 // x = hi + lo with hi = fp16(x), lo = fp16(x - hi): 22 significant bits kept.
 __global__ void split_f32_kernel(const float* __restrict__ x, __half* __restrict__ hi, __half* __restrict__ lo, long long n4) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
     const float4 v = reinterpret_cast<const float4*>(x)[i];
     const __half h0 = __float2half_rn(v.x), h1 = __float2half_rn(v.y), h2 = __float2half_rn(v.z), h3 = __float2half_rn(v.w);
@@ -648,6 +640,8 @@ extern "C" int bxl_gemm_split_f32(const float* A, const float* B, float* C, int 
 namespace bxl {
 // [C_out][C_in][3][3] -> [C_out][ky][kx][C_in]  (K index = tap*C_in + c)
 __global__ void conv_weight_pack_kernel(const __half* __restrict__ w, __half* __restrict__ out, int cout, int cin) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long total = (long long)cout * cin * 9;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const int c = i % cin;

@@ -30,6 +30,8 @@ constexpr int kGnMaxC = 4096;
 __global__ void __launch_bounds__(512) groupnorm_stats_kernel(const __half* __restrict__ x, long long img_stride, int HW,
                                                               int C, int G, int parts, float* __restrict__ partials,
                                                               int* __restrict__ ticket, float* __restrict__ moments, int B) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float s_ch[];  // [2][C] per-channel sum / sum of squares
   __shared__ int s_last;
   const int vecs = C / 8;               // 16-byte vectors per pixel
@@ -102,6 +104,8 @@ __global__ void __launch_bounds__(512) groupnorm_apply_kernel(const __half* __re
                                                               const float* __restrict__ fresh, GnPeers peers, int n_peers,
                                                               int own, int mode, float eps, const __half* __restrict__ gamma,
                                                               const __half* __restrict__ beta, int silu, int parts) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float s_ab[];  // [2][C]: scale, shift per channel
   __shared__ float s_mean[kGnMaxGroups], s_rstd[kGnMaxGroups];
   const int img = blockIdx.y;
@@ -214,9 +218,9 @@ extern "C" int bxl_groupnorm_stats_f16(const void* x, long long img_stride, int 
   const int threads = gn_threads(C), parts = gn_parts(HW, C, B);
   int* ticket = static_cast<int*>(scratch);
   float* partials = reinterpret_cast<float*>(static_cast<char*>(scratch) + 256);
-  groupnorm_stats_kernel<<<dim3(parts, B), threads, 2 * C * sizeof(float), (cudaStream_t)stream>>>(
-      static_cast<const __half*>(x), img_stride, HW, C, G, parts, partials, ticket, moments, B);
-  return check_cuda(cudaGetLastError(), "groupnorm_stats_kernel launch");
+  return launch_kernel("groupnorm_stats_kernel launch", groupnorm_stats_kernel, dim3(parts, B), dim3(threads), 2 * C * sizeof(float),
+                       (cudaStream_t)stream, 1, static_cast<const __half*>(x), img_stride, HW, C, G, parts, partials, ticket,
+                       moments, B);
 }
 
 extern "C" int bxl_groupnorm_apply_f16(const void* x, void* y, long long img_stride, int B, int HW, int C, int G,
@@ -238,10 +242,10 @@ extern "C" int bxl_groupnorm_apply_f16(const void* x, void* y, long long img_str
   const int cap = max(1, (sm_count() * 8) / B);
   if (parts > cap) parts = cap;
   if (parts < 1) parts = 1;
-  groupnorm_apply_kernel<<<dim3(parts, B), threads, 2 * C * sizeof(float), (cudaStream_t)stream>>>(
-      static_cast<const __half*>(x), static_cast<__half*>(y), img_stride, HW, C, G, B, fresh_moments, peers,
-      mode == 0 ? 0 : n_peers, own, mode, eps, static_cast<const __half*>(gamma), static_cast<const __half*>(beta), silu, parts);
-  return check_cuda(cudaGetLastError(), "groupnorm_apply_kernel launch");
+  return launch_kernel("groupnorm_apply_kernel launch", groupnorm_apply_kernel, dim3(parts, B), dim3(threads), 2 * C * sizeof(float),
+                       (cudaStream_t)stream, 1, static_cast<const __half*>(x), static_cast<__half*>(y), img_stride, HW, C, G, B,
+                       fresh_moments, peers, mode == 0 ? 0 : n_peers, own, mode, eps, static_cast<const __half*>(gamma),
+                       static_cast<const __half*>(beta), silu, parts);
 }
 
 // ---- statistics without caller-provided scratch ------------------------------------

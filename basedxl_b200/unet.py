@@ -82,7 +82,8 @@ class BasedXLUnet(BaseModel):
             )
         super().__init__(model, cfg)
         self.cuda_graph = False
-        self._graphed = None
+        self._graphed = None        # displaced steps (single GPU: every step)
+        self._graphed_sync = None   # synchronous warm-up steps of a patch-parallel run
 
     def enable_cuda_graph(self, enabled: bool = True):
         """Replay one captured CUDA graph per denoising step instead of launching
@@ -92,9 +93,10 @@ class BasedXLUnet(BaseModel):
 
     def release_graph(self):
         """Drop the captured step graph (call before destroying the process group)."""
-        if getattr(self, "_graphed", None) is not None:
-            self._graphed.release()
-        self._graphed = None
+        for slot in ("_graphed", "_graphed_sync"):
+            if getattr(self, slot, None) is not None:
+                getattr(self, slot).release()
+            setattr(self, slot, None)
 
     def patch_linear_layers(self, model: nn.Module):
         for _name, module in model.named_modules():
@@ -211,17 +213,27 @@ class BasedXLUnet(BaseModel):
             else:
                 output = self.model(sample, timestep, encoder_hidden_states, added_cond_kwargs=added_cond_kwargs, return_dict=False)[0]
         else:
-            # Displaced steps repeat the same launch sequence every step, so they are
-            # replayed from a graph; the synchronous warm-up steps (blocking per-layer
-            # collectives, 5 per image) are launched eagerly.
-            displaced = (not self.patched) or self.counter > cfg.warmup_steps
-            if self.cuda_graph and displaced and isinstance(timestep, torch.Tensor):
-                if self._graphed is None:
-                    from .graph import GraphedStep
+            # Every step but the first of an image repeats one of two launch sequences: the
+            # synchronous one (steps 1..warmup_steps: blocking per-layer collectives) and the
+            # displaced one (later steps).  Each is captured once - kernels and collectives -
+            # and replayed.  Step 0 runs eagerly: it also refreshes the cross-attention K/V.
+            c = self.counter
+            graphable = self.cuda_graph and isinstance(timestep, torch.Tensor) and (c > 0 or not self.patched)
+            if graphable:
+                from .graph import GraphedStep
 
-                    # no eager rehearsal: it would publish this step's tensors a step early
-                    self._graphed = GraphedStep(self._step_multi, warmup_runs=0)
-                output = self._graphed(sample, timestep, encoder_hidden_states, added_cond_kwargs)
+                displaced = (not self.patched) or c > cfg.warmup_steps
+                slot = "_graphed" if displaced else "_graphed_sync"
+                if getattr(self, slot) is None:
+                    # capture does not execute anything, so no step is rehearsed (a rehearsal
+                    # would publish this step's tensors a step early); the layers' own step
+                    # counters select the path that is recorded
+                    for module in self.model.modules():
+                        if isinstance(module, BaseModule):
+                            module.set_counter(c)
+                    drain = displaced
+                    setattr(self, slot, GraphedStep(lambda s_, t_, e_, a_, d=drain: self._step_multi(s_, t_, e_, a_, drain=d), warmup_runs=0))
+                output = getattr(self, slot)(sample, timestep, encoder_hidden_states, added_cond_kwargs)
             else:
                 output = self._step_multi(sample, timestep, encoder_hidden_states, added_cond_kwargs, drain=False)
         self.counter += 1

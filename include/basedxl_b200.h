@@ -40,6 +40,11 @@ int bxl_device_status(int* code, int* site, int* block);
 
 int bxl_sm_count(void);
 
+/* Launch kernels with programmatic stream serialisation (each kernel's set-up
+ * overlaps the tail of the one before it on the stream).  On by default; BXL_PDL=0 in
+ * the environment, or this call with 0, turns it off.  No counterpart in the reference. */
+int bxl_set_pdl(int enabled);
+
 /* Test hook: force the GEMM / convolution tile width (multiple of 32, <= 256) and
  * K split (1, 2 or 4); 0 restores the built-in choice.  No counterpart in the
  * reference. */
