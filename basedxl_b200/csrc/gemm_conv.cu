@@ -5,8 +5,8 @@
 //     tiles are gathered by TMA row by row from three sources: the fresh local
 //     strip and the (stale) boundary rows of the strips above and below.
 //
-// Roles inside a CTA of 192 threads (one CTA per SM, tiles strided by grid):
-//   warp 0      TMA producer: fills a ring of {A 128x64, B BNx64} fp16 stages
+// Roles inside a CTA of 224 threads (one CTA per SM, tiles strided by grid):
+//   warps 0, 6  TMA producers (A and B operand): fill a ring of {A 128x64, B BNx64} fp16 stages
 //   warp 1      allocates tensor memory and issues tcgen05.mma (one lane)
 //   warps 2..5  epilogue: tcgen05.ld the fp32 accumulator, add bias/residual,
 //               convert and store; runs while the next tile's mainloop fills the
@@ -20,6 +20,8 @@
 // keeps all SMs busy when a strip's problem has only a handful of tiles.
 //
 // Roofline: tensor cores.  Algorithmic FLOPs per tile = 2*128*BN*K.
+#include <math.h>
+
 #include "bxl_common.cuh"
 #include "bxl_host.h"
 #include "../../include/basedxl_b200.h"
@@ -29,7 +31,7 @@ namespace bxl {
 constexpr int kBM = 128;           // tile rows (= TMEM lanes, UMMA M)
 constexpr int kBK = 64;            // K per stage: 64 fp16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;         // K of one tcgen05.mma.kind::f16
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 224;   // warp 0: A loads, warp 1: MMA, warps 2..5: epilogue, warp 6: B loads
 constexpr int kMaxSeg = 3;
 constexpr int kABytes = kBM * kBK * 2;       // 16 KB
 constexpr int kSmemBudget = 227 * 1024;      // dynamic shared memory available to one CTA
@@ -37,8 +39,9 @@ constexpr int kSmemMisc = 2048;              // alignment slack + barriers
 constexpr int kMaxStages = 8;
 
 struct alignas(64) GemmParams {
-  CUtensorMap a_map[kMaxSeg];  // GEMM: A of each segment.  conv: body, top halo, bottom halo
+  CUtensorMap a_map[kMaxSeg];  // GEMM: A of each segment.  conv: body (one row per copy), top halo, bottom halo
   CUtensorMap b_map[kMaxSeg];  // GEMM: B of each segment.  conv: [0] = packed weights
+  CUtensorMap a_rows_map;      // conv: body again, with a box of `th` rows (one copy per stage)
   // problem
   int M, N, K;                 // conv: M = B*H_out*W_out (unused), N = C_out, K = 9*C_in
   int nseg;                    // GEMM segments (1, or 3 for the split-operand product)
@@ -160,7 +163,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(full_bar(s), 1);
+      mbar_init(full_bar(s), 2);   // one arrival (with its byte count) from each of the two producers
       mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -198,13 +201,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
   const int first_tile = blockIdx.x / S;
   const int tile_step = gridDim.x / S;
 
-  if (warp == 0) {
-    // ======================= TMA producer =======================
+  if (warp == 0 || warp == 6) {
+    // ======================= TMA producers =======================
+    // Issuing a tiled copy occupies the issuing thread for a few hundred cycles, so the A
+    // and B operands are fed by two threads in different warps; both arrive on the stage's
+    // "full" barrier with the bytes they ordered.
+    const bool loads_a = (warp == 0);
     if (lane == 0) {
-      for (int s = 0; s < kMaxSeg; ++s) {
-        tma_prefetch_desc(&p.a_map[s]);
-        tma_prefetch_desc(&p.b_map[s]);
-      }
+      for (int s = 0; s < kMaxSeg; ++s) tma_prefetch_desc(loads_a ? &p.a_map[s] : &p.b_map[s]);
+      if (loads_a && kConv) tma_prefetch_desc(&p.a_rows_map);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -221,48 +226,65 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
           x0 = (r % p.tiles_x) * p.tw;
         }
         for (int kb = kb_begin; kb < kb_end; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.dev_status, 100)) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.dev_status, loads_a ? 100 : 101)) {
             ok = false;
             break;
           }
           const uint32_t a_dst = smem_base + stage * stage_bytes;
           const uint32_t b_dst = a_dst + kABytes;
-          mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
-          if (kConv) {
-            const int cchunks = p.cCin / kBK;
-            const int tap = kb / cchunks;
-            const int c0 = (kb % cchunks) * kBK;
-            const int ky = tap / 3, kx = tap % 3;
-            // input column of output column ox: stride*ox + kx - 1, addressed as
-            // (parity, half-column) = ((kx-1) mod stride, ox + floor((kx-1)/stride))
-            int par = 0, xoff = kx - 1;
-            if (p.cStride == 2) {
-              par = (kx == 1) ? 0 : 1;
-              xoff = (kx == 0) ? -1 : 0;
-            }
-            for (int t = 0; t < p.th; ++t) {
-              const int r_in = p.cStride * (y0 + t) + ky - 1;
-              const uint32_t dst = a_dst + t * p.tw * 128;
-              if (r_in == -1 && p.has_top) {
-                tma_load_5d(dst, &p.a_map[1], full_bar(stage), c0, par, x0 + xoff, 0, img);
-              } else if (r_in == p.cHin && p.has_bot) {
-                tma_load_5d(dst, &p.a_map[2], full_bar(stage), c0, par, x0 + xoff, 0, img);
-              } else {
-                // rows outside [0, H) are zero-filled by the copy engine
-                tma_load_5d(dst, &p.a_map[0], full_bar(stage), c0, par, x0 + xoff, r_in, img);
+          if (loads_a) {
+            mbar_arrive_expect_tx(full_bar(stage), kABytes);
+            if (kConv) {
+              const int cchunks = p.cCin / kBK;
+              const int tap = kb / cchunks;
+              const int c0 = (kb % cchunks) * kBK;
+              const int ky = tap / 3, kx = tap % 3;
+              // input column of output column ox: stride*ox + kx - 1, addressed as
+              // (parity, half-column) = ((kx-1) mod stride, ox + floor((kx-1)/stride))
+              int par = 0, xoff = kx - 1;
+              if (p.cStride == 2) {
+                par = (kx == 1) ? 0 : 1;
+                xoff = (kx == 0) ? -1 : 0;
               }
-            }
-            tma_load_2d(b_dst, &p.b_map[0], full_bar(stage), kb * kBK, n0);
-          } else {
-            const int seg = kb / kb_per_seg;
-            const int k0 = (kb % kb_per_seg) * kBK;
-            tma_load_2d(a_dst, &p.a_map[seg], full_bar(stage), k0, tm * kBM);
-            if (p.b_kn) {
-              // B[K,N]: one 64(n) x 64(k) box per 64 output columns
-              for (int j = 0; j < BN / 64; ++j)
-                tma_load_2d(b_dst + j * 8192, &p.b_map[seg], full_bar(stage), n0 + j * 64, k0);
+              const int r_first = p.cStride * y0 + ky - 1;
+              const int r_last = p.cStride * (y0 + p.th - 1) + ky - 1;
+              const bool touches_halo = (p.has_top && r_first < 0) || (p.has_bot && r_last >= p.cHin);
+              if (p.cStride == 1 && !touches_halo) {
+                // all th input rows come from the body (rows outside [0, H) are zero-filled by
+                // the copy engine): one copy for the whole A tile
+                tma_load_5d(a_dst, &p.a_rows_map, full_bar(stage), c0, par, x0 + xoff, r_first, img);
+              } else {
+                for (int t = 0; t < p.th; ++t) {
+                  const int r_in = p.cStride * (y0 + t) + ky - 1;
+                  const uint32_t dst = a_dst + t * p.tw * 128;
+                  if (r_in == -1 && p.has_top) {
+                    tma_load_5d(dst, &p.a_map[1], full_bar(stage), c0, par, x0 + xoff, 0, img);
+                  } else if (r_in == p.cHin && p.has_bot) {
+                    tma_load_5d(dst, &p.a_map[2], full_bar(stage), c0, par, x0 + xoff, 0, img);
+                  } else {
+                    tma_load_5d(dst, &p.a_map[0], full_bar(stage), c0, par, x0 + xoff, r_in, img);
+                  }
+                }
+              }
             } else {
-              tma_load_2d(b_dst, &p.b_map[seg], full_bar(stage), k0, n0);
+              const int seg = kb / kb_per_seg;
+              const int k0 = (kb % kb_per_seg) * kBK;
+              tma_load_2d(a_dst, &p.a_map[seg], full_bar(stage), k0, tm * kBM);
+            }
+          } else {
+            mbar_arrive_expect_tx(full_bar(stage), BN * 128);
+            if (kConv) {
+              tma_load_2d(b_dst, &p.b_map[0], full_bar(stage), kb * kBK, n0);
+            } else {
+              const int seg = kb / kb_per_seg;
+              const int k0 = (kb % kb_per_seg) * kBK;
+              if (p.b_kn) {
+                // B[K,N]: one 64(n) x 64(k) box per 64 output columns
+                for (int j = 0; j < BN / 64; ++j)
+                  tma_load_2d(b_dst + j * 8192, &p.b_map[seg], full_bar(stage), n0 + j * 64, k0);
+              } else {
+                tma_load_2d(b_dst, &p.b_map[seg], full_bar(stage), k0, n0);
+              }
             }
           }
           if (++stage == p.stages) {
@@ -450,10 +472,11 @@ static int stages_for(int bn, int split) {
   return st;
 }
 
-// Pick the tile width and the K split that minimise a simple time model, in units
-// of one 128-column k-block: rounds x (k-blocks per unit x cost(bn) + epilogue) + fill.
-// A wider tile moves fewer operand bytes per FLOP; a narrower one or a K split
-// fills more of the SMs when the problem has few tiles.
+// Pick the tile width and the K split that minimise a time model calibrated on B200.
+// One CTA streams its operands at ~98 KB/us from L2 (the per-SM fill rate is what
+// bounds these kernels, not the tensor pipe), so a k-block of a 128 x bn tile costs
+// max(mma(bn), (16 KB + bn*128 B) / 98 KB/us); a wider tile moves fewer bytes per FLOP,
+// a narrower one or a K split spreads the stream over more SMs when there are few tiles.
 static TileConfig choose_tiles(int tiles_m, int N, int num_kb, bool b_kn, int force_bn = 0, int force_split = 0) {
   const int sms = sm_count();
   TileConfig best{128, 1, stages_for(128, 1)};
@@ -470,10 +493,11 @@ static TileConfig choose_tiles(int tiles_m, int N, int num_kb, bool b_kn, int fo
       const int clusters = sms / split;
       const int par = tiles < clusters ? tiles : clusters;
       const int rounds = (tiles + par - 1) / par;
-      const double kb_cost = 0.30 + 0.70 * bn / 128.0;
+      const double kb_us = fmax(bn / 256.0 * 0.27, (16384.0 + bn * 128.0) / 98000.0);
       const double kb_unit = (num_kb + split - 1) / split;
-      const double epi = (bn / 128.0) * 3.0 / split + (split > 1 ? 3.0 : 0.0);
-      const double cost = rounds * (kb_unit * kb_cost + epi) + 8.0;
+      const double epi_us = 0.12 * (bn / 32.0) / split + (split > 1 ? 1.2 : 0.0);   // accumulator read-out (+ exchange)
+      const double fill_us = 1.0 + (st < 4 ? 0.5 : 0.0);                             // pipeline ramp per unit
+      const double cost = rounds * (kb_unit * kb_us + epi_us) + fill_us + 3.0;
       if (cost < best_cost - 1e-9) {
         best_cost = cost;
         best = TileConfig{bn, split, st};
@@ -690,6 +714,12 @@ extern "C" int bxl_conv3x3_halo_f16(const void* x, long long x_img_stride, const
     return encode_tmap_f16(m, base, 5, dims, str, box);
   };
   if (int rc = enc(&p.a_map[0], x, H_in, x_img_stride)) return rc;
+  {
+    uint64_t dims[5] = {(uint64_t)C_in, (uint64_t)stride, (uint64_t)Wh, (uint64_t)H_in, (uint64_t)B};
+    uint64_t str[4] = {(uint64_t)C_in * 2, (uint64_t)stride * C_in * 2, (uint64_t)W * C_in * 2, (uint64_t)x_img_stride * 2};
+    uint32_t box[5] = {kBK, 1, (uint32_t)tw, (uint32_t)th, 1};
+    if (int rc = encode_tmap_f16(&p.a_rows_map, x, 5, dims, str, box)) return rc;
+  }
   if (int rc = enc(&p.a_map[1], top ? top : x, 1, top ? halo_img_stride : x_img_stride)) return rc;
   if (int rc = enc(&p.a_map[2], bot ? bot : x, 1, bot ? halo_img_stride : x_img_stride)) return rc;
   const int K = 9 * C_in;

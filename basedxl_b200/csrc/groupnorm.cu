@@ -83,13 +83,19 @@ __global__ void __launch_bounds__(512) groupnorm_stats_kernel(const __half* __re
   __syncthreads();
   if (!s_last) return;
   __threadfence();
+  // fold the partials: one warp per (image, group, moment), lanes striding over the slabs so
+  // that the loads are independent; fixed summation order (lane-strided, then a shuffle tree)
   const float inv_n = 1.f / (float)((long long)cpg * HW);
-  for (int i = threadIdx.x; i < B * G * 2; i += blockDim.x) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  if (warp >= warps) return;  // a trailing partial warp takes no part in the warp-wide shuffles
+  for (int i = warp; i < B * G * 2; i += warps) {
     const int which = i % 2, g = (i / 2) % G, b = i / (2 * G);
     float acc = 0.f;
-    for (int q = 0; q < parts; ++q) acc += __ldcg(&partials[(((long long)b * parts + q) * G + g) * 2 + which]);
+    for (int q = lane; q < parts; q += 32) acc += __ldcg(&partials[(((long long)b * parts + q) * G + g) * 2 + which]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     // published layout [2][B][G]: first moments, then second moments
-    moments[((long long)which * B + b) * G + g] = acc * inv_n;
+    if (lane == 0) moments[((long long)which * B + b) * G + g] = acc * inv_n;
   }
 }
 
