@@ -58,6 +58,7 @@ struct alignas(64) GemmParams {
   void* C;
   long long ldc;
   int out_f32;
+  int geglu;                   // epilogue pairs columns: out[16c+i] = h[32c+i] * gelu(h[32c+16+i]), N_out = N/2
   // conv geometry
   int cB, cHin, cW, cCin, cStride, cHout, cWout;
   int tw, th;                  // tile = th rows x tw columns of output pixels (th*tw = 128)
@@ -86,6 +87,26 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, float (&f)[32],
 #pragma unroll
     for (int j = 0; j < 32; ++j)
       if (fullw || nb + j < p.N) f[j] += __half2float(br[nb + j]);
+  }
+  if (!kConv && p.geglu) {
+    // columns arrive interleaved in groups of 16 values + 16 gates (weight rows were permuted by the
+    // caller); N is a multiple of 32 here, so the chunk is always complete
+    __half* cr = static_cast<__half*>(p.C) + out_row * p.ldc + (nb >> 1);
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      uint4 u;
+      __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = q * 8 + 2 * j;
+        const float g0 = f[16 + i], g1 = f[16 + i + 1];
+        const float y0 = f[i] * (0.5f * g0 * (1.f + erff(g0 * 0.70710678118654752f)));
+        const float y1 = f[i + 1] * (0.5f * g1 * (1.f + erff(g1 * 0.70710678118654752f)));
+        h[j] = __floats2half2_rn(y0, y1);
+      }
+      *reinterpret_cast<uint4*>(cr + q * 8) = u;
+    }
+    return;
   }
   if (p.residual) {
     const __half* rr = p.residual + out_row * p.ldr + nb;
@@ -582,6 +603,43 @@ extern "C" int bxl_gemm_f16(const void* A, long long lda, const void* B, long lo
   p.dev_status = st;
   const int tiles = tiles_m * ((N + BN - 1) / BN);
   return launch<false>(p, tiles, (cudaStream_t)stream);
+}
+
+extern "C" int bxl_gemm_geglu_f16(const void* A, long long lda, const void* B, long long ldb, const void* bias, void* C,
+                                  long long ldc, int M, int N, int K, void* stream) {
+  if (!A || !B || !C) return fail(kErrInvalidArg, "bxl_gemm_geglu_f16: null operand");
+  if (M <= 0 || N <= 0 || K <= 0 || N % 32) return fail(kErrInvalidArg, "bxl_gemm_geglu_f16: N=%d must be a positive multiple of 32", N);
+  if (lda % 8 || ldb % 8 || ldc % 8 || lda < K || ldb < K || ldc < N / 2)
+    return fail(kErrInvalidArg, "bxl_gemm_geglu_f16: bad leading dimension");
+  if (!aligned16(A) || !aligned16(B) || !aligned16(C)) return fail(kErrInvalidArg, "bxl_gemm_geglu_f16: operands must be 16-byte aligned");
+  int* st = device_status_ptr();
+  if (!st) return fail(kErrCuda, "bxl_gemm_geglu_f16: no device status word");
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  const int tiles_m = (M + kBM - 1) / kBM;
+  const TileConfig tc = choose_tiles(tiles_m, N, (K + kBK - 1) / kBK, false, g_force_bn, g_force_split);
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    uint64_t str[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {kBK, kBM};
+    if (int rc = encode_tmap_f16(&p.a_map[0], A, 2, dims, str, box)) return rc;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+    uint64_t str[1] = {(uint64_t)ldb * 2};
+    uint32_t box[2] = {kBK, (uint32_t)tc.bn};
+    if (int rc = encode_tmap_f16(&p.b_map[0], B, 2, dims, str, box)) return rc;
+  }
+  for (int s = 1; s < kMaxSeg; ++s) {
+    p.a_map[s] = p.a_map[0];
+    p.b_map[s] = p.b_map[0];
+  }
+  p.M = M, p.N = N, p.K = K, p.nseg = 1, p.b_kn = 0;
+  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages;
+  p.bias = static_cast<const __half*>(bias);
+  p.C = C, p.ldc = ldc, p.out_f32 = 0, p.geglu = 1;
+  p.dev_status = st;
+  return launch<false>(p, tiles_m * ((N + tc.bn - 1) / tc.bn), (cudaStream_t)stream);
 }
 
 extern "C" int bxl_debug_force_tiles(int bn, int split) {

@@ -20,9 +20,13 @@ class GraphedStep:
     piece of host-side state as it found it (the same graph is replayed for
     every later step)."""
 
-    def __init__(self, fn, warmup_runs: int = 1):
+    def __init__(self, fn, warmup_runs: int = 1, on_condition_change=None):
         self.fn = fn
         self.warmup_runs = warmup_runs
+        # called eagerly with the static inputs before the first capture and whenever new
+        # conditioning has been copied in: refreshes whatever the graph reads but does not
+        # recompute (the cached cross-attention K/V)
+        self.on_condition_change = on_condition_change
         self.graph: torch.cuda.CUDAGraph | None = None
         self.static = None
         self.out = None
@@ -53,6 +57,8 @@ class GraphedStep:
             }
             self._cond_key = self._cond_id(ehs, added)
             s = self.static
+            if self.on_condition_change is not None:
+                self.on_condition_change(s["sample"], s["timestep"], s["ehs"], s["added"])
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
@@ -78,6 +84,8 @@ class GraphedStep:
                 for k, v in added.items():
                     s["added"][k].copy_(v)
                 self._cond_key = key
+                if self.on_condition_change is not None:
+                    self.on_condition_change(s["sample"], s["timestep"], s["ehs"], s["added"])
         self.graph.replay()
         self.replays += 1
         from . import _lib

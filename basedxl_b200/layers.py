@@ -87,6 +87,9 @@ class Attention(nn.Module):
         self.residual_connection = False
         self.rescale_output_factor = 1.0
         self._kv = None
+        self._ctx_kv = None   # cross-attention: K/V of the conditioning, reused across steps
+        self._ctx_key = None
+        self._ctx_ref = None
 
     def _fused_kv(self) -> nn.Linear:
         key = (self.to_k.weight.data_ptr(), self.to_k.weight._version, self.to_v.weight._version)
@@ -94,10 +97,28 @@ class Attention(nn.Module):
             self._kv = (key, fuse_kv(self.to_k, self.to_v))
         return self._kv[1]
 
+    def context_kv(self, ctx: torch.Tensor, force: bool = False) -> torch.Tensor:
+        """K/V projection of the conditioning, computed when the conditioning tensor changes
+        (new storage or a new version) and otherwise reused: it is the same for all denoising
+        steps of an image (what the reference's patched cross-attention does with its
+        ``kv_cache``, basedxl/modules/attn.py:74-78).  Refreshed IN PLACE so that a captured
+        step graph keeps reading valid storage."""
+        key = (ctx.data_ptr(), ctx._version, tuple(ctx.shape))
+        b, l, _ = ctx.shape
+        if self._ctx_kv is None or self._ctx_kv.shape[:2] != (b, l):
+            self._ctx_kv = _lin(self._fused_kv(), ctx)
+        elif force or key != self._ctx_key:
+            _lin(self._fused_kv(), ctx, out=self._ctx_kv.view(b * l, -1))
+        self._ctx_key = key
+        self._ctx_ref = ctx  # keeps the storage alive, so its address cannot be reused by another tensor
+        return self._ctx_kv
+
     def forward(self, hidden_states, encoder_hidden_states=None, scale: float = 1.0, *args, residual=None, **kwargs):
-        ctx = hidden_states if encoder_hidden_states is None else encoder_hidden_states
         q = _lin(self.to_q, hidden_states)
-        kv = _lin(self._fused_kv(), ctx)
+        if encoder_hidden_states is None:
+            kv = _lin(self._fused_kv(), hidden_states)
+        else:
+            kv = self.context_kv(encoder_hidden_states)
         o = ops.attention(q, [kv], self.heads)
         return _finish(self, o, hidden_states, residual)
 
@@ -110,6 +131,20 @@ def geglu(h):
     return ops.geglu(h if h.is_contiguous() else h.contiguous())
 
 
+def linear_geglu(layer: nn.Linear, x):
+    """GEGLU projection with the gate applied in the GEMM epilogue.  The interleaved copy of
+    the weight is cached on the layer (inference: parameters are frozen)."""
+    w = layer.weight
+    cache = getattr(layer, "_bxl_geglu", None)
+    if cache is None or cache[0] != (w.data_ptr(), w._version):
+        layer._bxl_geglu = ((w.data_ptr(), w._version), ops.geglu_interleave(w.detach(), None if layer.bias is None else layer.bias.detach()))
+    wi, bi = layer._bxl_geglu[1]
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    y = ops.gemm_geglu(x2 if x2.stride(1) == 1 else x2.contiguous(), wi, bi)
+    return y.view(*lead, wi.shape[0] // 2)
+
+
 def upsample2x(x):
     return as_nchw(ops.upsample2x(as_nhwc(x)))
 
@@ -120,5 +155,6 @@ class KernelLayers:
     Conv2d, GroupNorm, Linear, LayerNorm, Attention = Conv2d, GroupNorm, Linear, LayerNorm, Attention
     silu = staticmethod(silu)
     geglu = staticmethod(geglu)
+    linear_geglu = staticmethod(linear_geglu)
     upsample2x = staticmethod(upsample2x)
     memory_format = torch.channels_last

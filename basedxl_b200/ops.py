@@ -67,6 +67,34 @@ def linear(x, weight, bias=None, residual=None):
     return y.view(*lead, weight.shape[0])
 
 
+def geglu_interleave(weight: torch.Tensor, bias: torch.Tensor | None):
+    """Reorder the rows of a GEGLU projection ([2F, K]: F value rows then F gate rows) into
+    groups of 16 value rows followed by their 16 gate rows, the order ``gemm_geglu`` expects."""
+    F2 = weight.shape[0]
+    F = F2 // 2
+    assert F % 16 == 0
+    idx = torch.arange(F, device=weight.device).view(F // 16, 16)
+    perm = torch.cat([idx, idx + F], dim=1).reshape(-1)
+    return weight[perm].contiguous(), (None if bias is None else bias[perm].contiguous())
+
+
+def gemm_geglu(a, w_interleaved, bias_interleaved=None, out=None):
+    """``geglu(a @ W^T + b)`` in one kernel; ``w_interleaved`` from :func:`geglu_interleave`."""
+    _f16_cuda(a, "a"), _f16_cuda(w_interleaved, "w")
+    M, K = a.shape
+    N = w_interleaved.shape[0]
+    _req(w_interleaved.shape[1] == K and a.stride(1) == 1 and w_interleaved.stride(1) == 1, "gemm_geglu: bad operands")
+    if out is None:
+        out = torch.empty((M, N // 2), device=a.device, dtype=torch.float16)
+    l = _lib.lib()
+    _lib.check(
+        l.bxl_gemm_geglu_f16(_p(a), a.stride(0), _p(w_interleaved), w_interleaved.stride(0), _p(bias_interleaved), _p(out),
+                             out.stride(0), M, N, K, _stream()),
+        l,
+    )
+    return out
+
+
 def gemm_split_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """fp32 ``a[M,K] @ b[K,N]`` through the split-operand tensor-core product."""
     _req(a.is_cuda and a.dtype == torch.float32 and b.dtype == torch.float32, "gemm_split_f32: CUDA fp32 operands")

@@ -129,7 +129,8 @@ class FeedForward(nn.Module):
         self.out = L.Linear(dim * 4, dim)
 
     def forward(self, x, residual):
-        h = self.L.geglu(self.proj(x))
+        fused_proj = getattr(self.L, "linear_geglu", None)
+        h = fused_proj(self.proj, x) if fused_proj is not None and type(self.proj) is self.L.Linear else self.L.geglu(self.proj(x))
         if _fused(self.out):
             return self.out(h, residual=residual)
         return self.out(h) + residual

@@ -150,6 +150,15 @@ class BasedXLUnet(BaseModel):
         cm.create_buffer()
         self.set_counter(0)
 
+    @torch.no_grad()
+    def _refresh_context(self, sample, timestep, encoder_hidden_states, added_cond_kwargs):
+        """Recompute, in place, the conditioning K/V that un-patched cross-attention layers cache."""
+        _, _, ehs, _ = self._slice_batch(sample, timestep, encoder_hidden_states, added_cond_kwargs)
+        ctx = ehs.to(next(self.model.parameters()).dtype)
+        for m in self.model.modules():
+            if hasattr(m, "context_kv") and getattr(m, "is_cross", False):
+                m.context_kv(ctx, force=True)
+
     def _slice_batch(self, sample, timestep, encoder_hidden_states, added_cond_kwargs):
         cfg = self.basedxl_config
         if not (cfg.use_cfg and cfg.world_size > 1):
@@ -207,7 +216,8 @@ class BasedXLUnet(BaseModel):
                     from .graph import GraphedStep
 
                     self._graphed = GraphedStep(
-                        lambda s, t, e, a: self.model(s, t, e, added_cond_kwargs=a, return_dict=False)[0]
+                        lambda s, t, e, a: self.model(s, t, e, added_cond_kwargs=a, return_dict=False)[0],
+                        on_condition_change=self._refresh_context,
                     )
                 output = self._graphed(sample, timestep, encoder_hidden_states, added_cond_kwargs)
             else:
@@ -232,7 +242,8 @@ class BasedXLUnet(BaseModel):
                         if isinstance(module, BaseModule):
                             module.set_counter(c)
                     drain = displaced
-                    setattr(self, slot, GraphedStep(lambda s_, t_, e_, a_, d=drain: self._step_multi(s_, t_, e_, a_, drain=d), warmup_runs=0))
+                    setattr(self, slot, GraphedStep(lambda s_, t_, e_, a_, d=drain: self._step_multi(s_, t_, e_, a_, drain=d),
+                                                    warmup_runs=0, on_condition_change=self._refresh_context))
                 output = getattr(self, slot)(sample, timestep, encoder_hidden_states, added_cond_kwargs)
             else:
                 output = self._step_multi(sample, timestep, encoder_hidden_states, added_cond_kwargs, drain=False)

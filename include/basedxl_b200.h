@@ -65,6 +65,15 @@ int bxl_gemm_f16(const void* A, long long lda, const void* B, long long ldb, int
                  const void* residual, long long ldr, void* C, long long ldc, int out_f32, int M, int N, int K,
                  void* stream);
 
+/* Feed-forward input projection with the GEGLU gate fused into the epilogue:
+ * h = A[M,K] * B[N,K]^T + bias[N]; out[m, 16c+i] = h[m, 32c+i] * gelu(h[m, 32c+16+i]), i < 16.
+ * B and bias are given with their rows INTERLEAVED in groups of 16 value rows followed by
+ * the 16 matching gate rows (done once per layer); C is [M, N/2] fp16.  Exact erf GELU.
+ * Replaces: the GEGLU projection + chunk + gelu + multiply of the host UNet's feed-forward
+ * blocks (the elementwise traffic between the patched operators). */
+int bxl_gemm_geglu_f16(const void* A, long long lda, const void* B, long long ldb, const void* bias, void* C,
+                       long long ldc, int M, int N, int K, void* stream);
+
 /* Split-operand product of fp32 matrices: A[M,K] and B[K,N] (row-major fp32) are
  * each split into fp16 high and low parts and C = Ah*Bh + Ah*Bl + Al*Bh is
  * accumulated in one fp32 tensor-memory accumulator; C is fp32 [M,N].

@@ -36,6 +36,19 @@ def gemm(a, b, bias=None, residual=None, out=None, b_is_kn=False, out_f32=False)
     return y
 
 
+def gemm_geglu(a, w_interleaved, bias_interleaved=None, out=None):
+    h = a @ w_interleaved.t()
+    if bias_interleaved is not None:
+        h = h + bias_interleaved
+    m, n = h.shape
+    h = h.view(m, n // 32, 2, 16)
+    y = (h[:, :, 0] * F.gelu(h[:, :, 1])).reshape(m, n // 2)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
 def conv_weight_pack(w):
     co, ci = w.shape[:2]
     return w.permute(0, 2, 3, 1).reshape(co, 9 * ci).contiguous()
@@ -118,6 +131,6 @@ def install():
     """Replace the kernel wrappers of ``basedxl_b200.ops`` by the functions above."""
     from basedxl_b200 import ops
 
-    for name in ("gemm", "conv_weight_pack", "conv3x3", "halo_pack", "groupnorm_stats", "groupnorm_apply", "attention",
+    for name in ("gemm", "gemm_geglu", "conv_weight_pack", "conv3x3", "halo_pack", "groupnorm_stats", "groupnorm_apply", "attention",
                  "upsample2x", "layernorm", "geglu"):
         setattr(ops, name, globals()[name])

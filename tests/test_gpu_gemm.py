@@ -152,3 +152,20 @@ def test_auto_tiling_on_every_per_rank_linear_shape(tokens):
         err = float((y.float() - ref).norm() / ref.norm())
         assert torch.isfinite(y).all() and err < 2e-3, f"tokens={tokens} K={K} N={N}: rel-L2 {err:.3e}"
     _lib.device_status()
+
+
+@pytest.mark.parametrize("M,K,F", [(300, 640, 2560), (2048, 1280, 5120), (64, 128, 512)])
+def test_gemm_with_fused_geglu(M, K, F):
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    g = torch.Generator().manual_seed(M + F)
+    x = h16(torch.randn(M, K, generator=g))
+    w = h16(torch.randn(2 * F, K, generator=g) / K**0.5)
+    b = h16(torch.randn(2 * F, generator=g))
+    h = x @ w.t() + b
+    ref = h[:, :F] * torch.nn.functional.gelu(h[:, F:])
+    wi, bi = ops.geglu_interleave(w.half().to(dev), b.half().to(dev))
+    y = ops.gemm_geglu(x.half().to(dev), wi, bi)
+    _lib.device_status()
+    assert y.shape == (M, F)
+    assert_close(y, ref, what=f"gemm+geglu {M}x{K}x{F}")
