@@ -12,13 +12,18 @@
 //               the two query tiles g = 0, 1:
 //                 S_g     = Q_g K_j^T      (128x128, K-major operands)
 //                 Opart_g = P_g V_j        (128x64, V consumed MN-major as stored)
+//                 L_g     = P_g 1          (128x16: row sums of the rounded P)
+//               O_g and L_g accumulate in tensor memory over all K/V tiles.
 //   warps 2..5  softmax group 0, warps 6..9 softmax group 1: thread r owns query
-//               row r of its tile (= TMEM lane r): running max and sum,
-//               P -> fp16 -> swizzled shared memory, and the fp32 output
-//               accumulator (64 registers), rescaled on the fly.  Exponentials are
-//               taken two per MUFU operation (ex2 on packed fp16, argument formed in
-//               fp32); the row sums of the rounded P come from a 16-column product
-//               with a matrix of ones on the tensor core.
+//               row r of its tile (= TMEM lane r).  Per K/V tile it reads its row of
+//               S once (128 registers), releases S at once so the next Q K^T can
+//               start, takes the row maximum, forms P = exp2(S*scale - m) two values
+//               per MUFU operation (ex2 on packed fp16, argument formed in fp32) and
+//               writes P to swizzled shared memory.  The running maximum m is only
+//               raised when the tile maximum exceeds it by more than 8 (a factor of
+//               256, harmless in fp16/fp32); only then O and L are rescaled in tensor
+//               memory (tcgen05.ld / multiply / tcgen05.st).  The result is exact:
+//               O and L always refer to the same m.
 // While one group runs its softmax the tensor core works for the other one.
 //
 // Roofline: tensor cores; algorithmic FLOPs = 4 * L_q * L_kv * 64 per (image, head).
@@ -78,6 +83,21 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+      "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+      "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+      "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_1(uint32_t taddr, uint32_t v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ uint32_t tmem_ld_1(uint32_t taddr) {
   uint32_t r;
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
@@ -89,13 +109,14 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t bar_base = smem_base + AttnSmem::kBar;
-  // barriers: q_full, kv_full[3], kv_empty[3], s_full[2], o_full[2], p_full[2]
+  // barriers: q_full, kv_full[3], kv_empty[3], s_full[2], o_full[2], p_full[2], s_free[2]
   const uint32_t q_full = bar_base;
   auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bar_base + 8u * (1 + kKvStages + s); };
   auto s_full = [&](int g) { return bar_base + 8u * (1 + 2 * kKvStages + g); };
   auto o_full = [&](int g) { return bar_base + 8u * (3 + 2 * kKvStages + g); };
   auto p_full = [&](int g) { return bar_base + 8u * (5 + 2 * kKvStages + g); };
+  auto s_free = [&](int g) { return bar_base + 8u * (7 + 2 * kKvStages + g); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + AttnSmem::kBar + 512);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + AttnSmem::kBar + 520);
 
@@ -124,6 +145,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
       mbar_init(s_full(g), 1);
       mbar_init(o_full(g), 1);
       mbar_init(p_full(g), 128);
+      mbar_init(s_free(g), 128);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -199,7 +221,16 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
         const uint64_t vdesc = make_smem_desc_sw128(smem_base + AttnSmem::kV + st * 16384, 16, 1024);
         if (j + 1 < n_tiles && !wait_kv(j + 1)) break;
         for (int g = 0; g < n_groups && ok; ++g) {
-          // P_g(j) is in shared memory, S_g and Opart_g are free again
+          if (j + 1 < n_tiles) {
+            // the softmax group has copied S_g(j) into registers: the next Q K^T may overwrite it
+            if (!mbar_wait(s_free(g), j & 1u, abort_flag, p.dev_status, 503)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            issue_s(j + 1, g);
+          }
+          // P_g(j) is in shared memory; O_g and L_g carry the right scale
           if (!mbar_wait(p_full(g), j & 1u, abort_flag, p.dev_status, 502)) {
             ok = false;
             break;
@@ -208,23 +239,23 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
           const uint64_t pdesc0 = make_smem_desc_sw128(smem_base + AttnSmem::kP + g * 32768, 16, 1024);
           const uint64_t pdesc1 = make_smem_desc_sw128(smem_base + AttnSmem::kP + g * 32768 + 16384, 16, 1024);
           const uint32_t d = tmem_base + 256 + g * 64;
+          const uint32_t dl = tmem_base + 384 + g * 16;
+          const uint32_t acc = (j != 0);
 #pragma unroll
           for (int k = 0; k < kTileKV / 16; ++k) {
             // tokens 16k..16k+15: P columns are K-major (32 B per step inside a 64-column half),
             // V rows advance by 16 x 128 B
             const uint64_t pd = ((k < 4) ? pdesc0 : pdesc1) + 2u * (k & 3);
-            umma_f16(d, pd, vdesc + 128u * k, idesc_o, k != 0);
+            umma_f16(d, pd, vdesc + 128u * k, idesc_o, acc | k);
           }
           // row sums of the rounded P on the tensor core, exact in fp32
-          const uint32_t dl = tmem_base + 384 + g * 16;
 #pragma unroll
           for (int k = 0; k < kTileKV / 16; ++k) {
             const uint64_t pd = ((k < 4) ? pdesc0 : pdesc1) + 2u * (k & 3);
-            umma_f16(dl, pd, ((k < 4) ? ones0 : ones1) + 2u * (k & 3), idesc_l, k != 0);
+            umma_f16(dl, pd, ((k < 4) ? ones0 : ones1) + 2u * (k & 3), idesc_l, acc | k);
           }
           umma_commit(o_full(g));
           if (g == n_groups - 1) umma_commit(kv_empty(st));  // K_j and V_j are no longer needed
-          if (j + 1 < n_tiles) issue_s(j + 1, g);
         }
       }
     }
@@ -237,28 +268,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
       const uint32_t s_addr = t_lane + g * 128;
       const uint32_t o_addr = t_lane + 256 + g * 64;
-      float o_acc[kHeadDim];
-#pragma unroll
-      for (int i = 0; i < kHeadDim; ++i) o_acc[i] = 0.f;
-      float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+      const uint32_t l_addr = t_lane + 384 + g * 16;
+      float m_run = -INFINITY;   // running row maximum in the exp2 domain (score * scale * log2 e)
       uint8_t* p_smem = smem_gen + AttnSmem::kP + g * 32768;
       const float sc = p.scale_log2e;
+      constexpr float kRaise = 8.f;  // raise m only when the tile maximum exceeds it by 2^8
       bool ok = true;
-      const uint32_t l_addr = t_lane + 384 + g * 16;
-      // O = O*alpha + Opart, l = l*alpha + Lpart for the tile whose P V product just finished
-      auto add_opart = [&]() {
-        uint32_t v0[32], v1[32];
-        tmem_ld_32x32(o_addr, v0);
-        tmem_ld_32x32(o_addr + 32, v1);
-        const uint32_t lp = tmem_ld_1(l_addr);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          o_acc[i] = fmaf(o_acc[i], alpha_prev, __uint_as_float(v0[i]));
-          o_acc[32 + i] = fmaf(o_acc[32 + i], alpha_prev, __uint_as_float(v1[i]));
-        }
-        l_run = fmaf(l_run, alpha_prev, __uint_as_float(lp));
-      };
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int t0 = (j % tiles_per_slot) * kTileKV;
         const int valid = min(kTileKV, p.L_slot - t0);
@@ -268,28 +283,59 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
         }
         __syncwarp();
         tc_fence_after_sync();
-        // pass 1: row maximum
+        // the whole row of S into registers, then hand the buffer back
+        uint32_t v0[32], v1[32], v2[32], v3[32];
+        tmem_ld_32x32(s_addr, v0);
+        tmem_ld_32x32(s_addr + 32, v1);
+        tmem_ld_32x32(s_addr + 64, v2);
+        tmem_ld_32x32(s_addr + 96, v3);
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        mbar_arrive(s_free(g));
         float m_tile = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          uint32_t v0[32], v1[32];
-          tmem_ld_32x32(s_addr + c * 64, v0);
-          tmem_ld_32x32(s_addr + c * 64 + 32, v1);
-          tmem_ld_wait();
-          if (valid == kTileKV) {
+        if (valid == kTileKV) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) m_tile = max3(m_tile, __uint_as_float(v0[i]), __uint_as_float(v1[i]));
-          } else {
+          for (int i = 0; i < 32; ++i) {
+            m_tile = max3(m_tile, __uint_as_float(v0[i]), __uint_as_float(v1[i]));
+            m_tile = max3(m_tile, __uint_as_float(v2[i]), __uint_as_float(v3[i]));
+          }
+        } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              if (c * 64 + i < valid) m_tile = fmaxf(m_tile, __uint_as_float(v0[i]));
-              if (c * 64 + 32 + i < valid) m_tile = fmaxf(m_tile, __uint_as_float(v1[i]));
-            }
+          for (int i = 0; i < 32; ++i) {
+            if (i < valid) m_tile = fmaxf(m_tile, __uint_as_float(v0[i]));
+            if (32 + i < valid) m_tile = fmaxf(m_tile, __uint_as_float(v1[i]));
+            if (64 + i < valid) m_tile = fmaxf(m_tile, __uint_as_float(v2[i]));
+            if (96 + i < valid) m_tile = fmaxf(m_tile, __uint_as_float(v3[i]));
           }
         }
         const float m_new = fmaxf(m_run, m_tile * sc);
-        const float alpha = fast_exp2(m_run - m_new);  // 0 on the first tile (m_run = -inf)
-        // the previous tile's P V product: frees the P buffer and delivers Opart(j-1), Lpart(j-1)
+        float alpha = 1.f;
+        if (j == 0) {
+          m_run = m_new;  // O and L start from zero: nothing to rescale
+        } else if (m_new > m_run + kRaise) {
+          alpha = fast_exp2(m_run - m_new);
+          m_run = m_new;
+        }
+        const bool rescale = __any_sync(0xffffffffu, alpha != 1.f);
+        // P = exp2(S*scale - m) as packed fp16
+        uint32_t pk[64];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          pk[i] = exp2_f16x2(fmaf(__uint_as_float(v0[2 * i]), sc, -m_run), fmaf(__uint_as_float(v0[2 * i + 1]), sc, -m_run));
+          pk[16 + i] = exp2_f16x2(fmaf(__uint_as_float(v1[2 * i]), sc, -m_run), fmaf(__uint_as_float(v1[2 * i + 1]), sc, -m_run));
+          pk[32 + i] = exp2_f16x2(fmaf(__uint_as_float(v2[2 * i]), sc, -m_run), fmaf(__uint_as_float(v2[2 * i + 1]), sc, -m_run));
+          pk[48 + i] = exp2_f16x2(fmaf(__uint_as_float(v3[2 * i]), sc, -m_run), fmaf(__uint_as_float(v3[2 * i + 1]), sc, -m_run));
+        }
+        if (valid != kTileKV) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const int col = 2 * i;
+            if (col >= valid) pk[i] = 0u;
+            else if (col + 1 >= valid) pk[i] &= 0x0000FFFFu;
+          }
+        }
+        // the previous tile's P V product must have finished: it read the P buffer, and O / L
+        // are only touched between two products
         if (j > 0) {
           if (!mbar_wait(o_full(g), (j - 1) & 1u, abort_flag, p.dev_status, 601)) {
             ok = false;
@@ -297,41 +343,34 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
           }
           __syncwarp();
           tc_fence_after_sync();
-          add_opart();
-        }
-        // pass 2: P = exp2(S*scale - m) as fp16 into swizzled shared memory (the row sum is
-        // taken by the tensor core from the same rounded values)
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          uint32_t v0[32], v1[32];
-          tmem_ld_32x32(s_addr + c * 64, v0);
-          tmem_ld_32x32(s_addr + c * 64 + 32, v1);
-          tmem_ld_wait();
-          uint32_t packed[32];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            packed[i] = exp2_f16x2(fmaf(__uint_as_float(v0[2 * i]), sc, -m_new), fmaf(__uint_as_float(v0[2 * i + 1]), sc, -m_new));
-            packed[16 + i] = exp2_f16x2(fmaf(__uint_as_float(v1[2 * i]), sc, -m_new), fmaf(__uint_as_float(v1[2 * i + 1]), sc, -m_new));
-          }
-          if (valid != kTileKV) {
+          if (rescale) {
+            uint32_t o0[32], o1[32];
+            tmem_ld_32x32(o_addr, o0);
+            tmem_ld_32x32(o_addr + 32, o1);
+            const uint32_t lp = tmem_ld_1(l_addr);
+            tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              const int col = c * 64 + 2 * i;
-              if (col >= valid) packed[i] = 0u;
-              else if (col + 1 >= valid) packed[i] &= 0x0000FFFFu;
+              o0[i] = __float_as_uint(__uint_as_float(o0[i]) * alpha);
+              o1[i] = __float_as_uint(__uint_as_float(o1[i]) * alpha);
             }
+            tmem_st_32x32(o_addr, o0);
+            tmem_st_32x32(o_addr + 32, o1);
+            tmem_st_1(l_addr, __float_as_uint(__uint_as_float(lp) * alpha));
+            tmem_st_wait();
           }
-          // 64 columns = one 64-column half of the P tile: 8 chunks of 16 B
-          uint8_t* half_base = p_smem + c * 16384;
+        }
+        // two 64-column halves of the P tile, 8 chunks of 16 B each
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          uint8_t* half_base = p_smem + hf * 16384;
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
             *reinterpret_cast<uint4*>(half_base + sw128_offset(row, q)) =
-                make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                make_uint4(pk[hf * 32 + 4 * q], pk[hf * 32 + 4 * q + 1], pk[hf * 32 + 4 * q + 2], pk[hf * 32 + 4 * q + 3]);
           }
         }
-        m_run = m_new;
-        alpha_prev = alpha;
-        // publish P(j) (generic-proxy writes -> async proxy); S_g, Opart_g and Lpart_g are free
+        // publish P(j) (generic-proxy writes -> async proxy)
         fence_proxy_async_smem();
         tc_fence_before_sync();
         mbar_arrive(p_full(g));
@@ -341,19 +380,32 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
         if (mbar_wait(o_full(g), j & 1u, abort_flag, p.dev_status, 602)) {
           __syncwarp();
           tc_fence_after_sync();
-          add_opart();
+          uint32_t o0[32], o1[32];
+          tmem_ld_32x32(o_addr, o0);
+          tmem_ld_32x32(o_addr + 32, o1);
+          const uint32_t lp = tmem_ld_1(l_addr);
+          tmem_ld_wait();
           const int q_row = q_row0 + g * kTileQ + row;
           if (q_row < p.L_q) {
-            const float inv_l = 1.f / l_run;
+            const float inv_l = 1.f / __uint_as_float(lp);
             __half* dst = p.out + (long long)img * p.out_img_stride + (long long)q_row * p.ld_out + head * kHeadDim;
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
+            for (int q = 0; q < 4; ++q) {
               uint4 u;
               __half2* h = reinterpret_cast<__half2*>(&u);
 #pragma unroll
               for (int i = 0; i < 4; ++i)
-                h[i] = __floats2half2_rn(o_acc[q * 8 + 2 * i] * inv_l, o_acc[q * 8 + 2 * i + 1] * inv_l);
+                h[i] = __floats2half2_rn(__uint_as_float(o0[q * 8 + 2 * i]) * inv_l, __uint_as_float(o0[q * 8 + 2 * i + 1]) * inv_l);
               *reinterpret_cast<uint4*>(dst + q * 8) = u;
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 u;
+              __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                h[i] = __floats2half2_rn(__uint_as_float(o1[q * 8 + 2 * i]) * inv_l, __uint_as_float(o1[q * 8 + 2 * i + 1]) * inv_l);
+              *reinterpret_cast<uint4*>(dst + 32 + q * 8) = u;
             }
           }
         }
