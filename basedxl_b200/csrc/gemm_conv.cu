@@ -58,6 +58,12 @@ struct alignas(64) GemmParams {
   void* C;
   long long ldc;
   int out_f32;
+  // optional second destination: output columns >= n_split go to C2[:, col - n_split] (row stride ldc2);
+  // n_split is a multiple of 32 (0 = single destination).  Used to write q and k|v of one fused projection
+  // to different buffers (the K/V staging slot has its own row stride).
+  void* C2;
+  long long ldc2;
+  int n_split;
   int geglu;                   // epilogue pairs columns: out[16c+i] = h[32c+i] * gelu(h[32c+16+i]), N_out = N/2
   // conv geometry
   int cB, cHin, cW, cCin, cStride, cHout, cWout;
@@ -138,7 +144,9 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, float (&f)[32],
         if (nb + j < p.N) cr[j] = f[j];
     }
   } else {
-    __half* cr = static_cast<__half*>(p.C) + out_row * p.ldc + nb;
+    __half* cr = (!kConv && p.n_split && nb >= p.n_split)
+                     ? static_cast<__half*>(p.C2) + out_row * p.ldc2 + (nb - p.n_split)
+                     : static_cast<__half*>(p.C) + out_row * p.ldc + nb;
     if (fullw) {
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
@@ -603,6 +611,45 @@ extern "C" int bxl_gemm_f16(const void* A, long long lda, const void* B, long lo
   p.dev_status = st;
   const int tiles = tiles_m * ((N + BN - 1) / BN);
   return launch<false>(p, tiles, (cudaStream_t)stream);
+}
+
+extern "C" int bxl_gemm_dual_f16(const void* A, long long lda, const void* B, long long ldb, const void* bias, void* C1,
+                                 long long ldc1, int n1, void* C2, long long ldc2, int M, int N, int K, void* stream) {
+  if (!A || !B || !C1 || !C2) return fail(kErrInvalidArg, "bxl_gemm_dual_f16: null operand");
+  if (M <= 0 || N <= 0 || K <= 0 || n1 <= 0 || n1 >= N || n1 % 32 || N % 8)
+    return fail(kErrInvalidArg, "bxl_gemm_dual_f16: need 0 < n1 < N with n1 a multiple of 32 (n1=%d N=%d)", n1, N);
+  if (lda % 8 || ldb % 8 || ldc1 % 8 || ldc2 % 8 || lda < K || ldb < K || ldc1 < n1 || ldc2 < N - n1)
+    return fail(kErrInvalidArg, "bxl_gemm_dual_f16: bad leading dimension");
+  if (!aligned16(A) || !aligned16(B) || !aligned16(C1) || !aligned16(C2))
+    return fail(kErrInvalidArg, "bxl_gemm_dual_f16: operands must be 16-byte aligned");
+  int* st = device_status_ptr();
+  if (!st) return fail(kErrCuda, "bxl_gemm_dual_f16: no device status word");
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  const int tiles_m = (M + kBM - 1) / kBM;
+  const TileConfig tc = choose_tiles(tiles_m, N, (K + kBK - 1) / kBK, false, g_force_bn, g_force_split);
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    uint64_t str[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {kBK, kBM};
+    if (int rc = encode_tmap_f16(&p.a_map[0], A, 2, dims, str, box)) return rc;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+    uint64_t str[1] = {(uint64_t)ldb * 2};
+    uint32_t box[2] = {kBK, (uint32_t)tc.bn};
+    if (int rc = encode_tmap_f16(&p.b_map[0], B, 2, dims, str, box)) return rc;
+  }
+  for (int s = 1; s < kMaxSeg; ++s) {
+    p.a_map[s] = p.a_map[0];
+    p.b_map[s] = p.b_map[0];
+  }
+  p.M = M, p.N = N, p.K = K, p.nseg = 1, p.b_kn = 0;
+  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages;
+  p.bias = static_cast<const __half*>(bias);
+  p.C = C1, p.ldc = ldc1, p.C2 = C2, p.ldc2 = ldc2, p.n_split = n1;
+  p.dev_status = st;
+  return launch<false>(p, tiles_m * ((N + tc.bn - 1) / tc.bn), (cudaStream_t)stream);
 }
 
 extern "C" int bxl_gemm_geglu_f16(const void* A, long long lda, const void* B, long long ldb, const void* bias, void* C,

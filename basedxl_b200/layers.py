@@ -14,7 +14,7 @@ import torch
 import torch.nn as nn
 
 from . import ops
-from .modules.attn import _finish, _lin, fuse_kv
+from .modules.attn import _finish, _lin, fuse_kv, qkv_project
 from .modules.base_module import as_nchw, as_nhwc
 from .modules.conv2d import check_conv, packed_weight
 
@@ -114,10 +114,13 @@ class Attention(nn.Module):
         return self._ctx_kv
 
     def forward(self, hidden_states, encoder_hidden_states=None, scale: float = 1.0, *args, residual=None, **kwargs):
-        q = _lin(self.to_q, hidden_states)
         if encoder_hidden_states is None:
-            kv = _lin(self._fused_kv(), hidden_states)
+            if type(self.to_q) is Linear and self.to_q.out_features % 32 == 0:
+                q, kv = qkv_project(self, self.to_q, self._fused_kv(), hidden_states)
+            else:
+                q, kv = _lin(self.to_q, hidden_states), _lin(self._fused_kv(), hidden_states)
         else:
+            q = _lin(self.to_q, hidden_states)
             kv = self.context_kv(encoder_hidden_states)
         o = ops.attention(q, [kv], self.heads)
         return _finish(self, o, hidden_states, residual)

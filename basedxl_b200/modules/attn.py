@@ -39,6 +39,36 @@ def fuse_kv(to_k: nn.Linear, to_v: nn.Linear) -> nn.Linear:
     return to_kv
 
 
+def fuse_qkv(to_q: nn.Linear, to_kv: nn.Linear):
+    """Stacked weight [W_q; W_k; W_v] (and bias) for the single-launch q | k|v projection."""
+    w = torch.cat([to_q.weight.detach(), to_kv.weight.detach()], dim=0).contiguous()
+    if (to_q.bias is None) != (to_kv.bias is None):
+        zq = to_q.bias if to_q.bias is not None else torch.zeros_like(to_q.weight[:, 0])
+        zk = to_kv.bias if to_kv.bias is not None else torch.zeros_like(to_kv.weight[:, 0])
+        b = torch.cat([zq.detach(), zk.detach()])
+    else:
+        b = None if to_q.bias is None else torch.cat([to_q.bias.detach(), to_kv.bias.detach()])
+    return w, b
+
+
+def qkv_project(owner, to_q: nn.Linear, to_kv: nn.Linear, x: torch.Tensor, kv_out=None):
+    """q and k|v of self-attention from one GEMM launch; ``kv_out`` (``[rows, 2C]`` view, any row
+    stride) receives k|v, e.g. this strip's staging slot.  The stacked weight is cached on
+    ``owner`` (inference: parameters are frozen)."""
+    key = (to_q.weight.data_ptr(), to_q.weight._version, to_kv.weight.data_ptr(), to_kv.weight._version)
+    cache = getattr(owner, "_bxl_qkv", None)
+    if cache is None or cache[0] != key:
+        owner._bxl_qkv = (key, fuse_qkv(to_q, to_kv))
+    w, b = owner._bxl_qkv[1]
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    c = to_q.out_features
+    q, kv = ops.gemm_dual(x2, w, c, bias=b, out2=kv_out)
+    return q.view(*lead, c), kv.view(*lead, 2 * c) if kv_out is None else None
+
+
 def _lin(layer: nn.Linear, x: torch.Tensor, residual=None, out=None) -> torch.Tensor:
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1])
@@ -99,24 +129,31 @@ class BasedXLSelfAttentionPP(BasedXLAttentionPP):
         assert self.comm_manager is not None
         n, idx = cfg.n_device_per_batch, cfg.split_idx()
         b, l, c = hidden_states.shape
-        q = _lin(attn.to_q, hidden_states)
-        if n == 1:
-            slots = [_lin(self.to_kv, hidden_states)]
-        elif self.buffer_list is None:
-            # no staging buffers yet: own K/V stands in for every strip (attn.py:132-133)
-            kv = _lin(self.to_kv, hidden_states)
-            slots = [kv] * n
-        elif self.counter <= cfg.warmup_steps:
-            kv = _lin(self.to_kv, hidden_states)
-            dist.all_gather(self.buffer_list, kv, group=cfg.batch_group, async_op=False)
-            slots = list(self.buffer_list)
-        else:
-            # fresh K/V is produced directly in the own staging slot; peers' slots are
-            # one step stale (attn.py:138-141)
+        fusable = isinstance(attn.to_q, nn.Linear) and c % 32 == 0
+        if n > 1 and self.buffer_list is not None and self.counter > cfg.warmup_steps:
+            # displaced step: fresh K/V is produced directly in the own staging slot; peers' slots
+            # are one step stale (attn.py:138-141)
             own = self.buffer_list[idx]
-            _lin(self.to_kv, hidden_states, out=own.view(b * l, -1))
+            if fusable:
+                q, _ = qkv_project(self, attn.to_q, self.to_kv, hidden_states, kv_out=own.view(b * l, -1))
+            else:
+                q = _lin(attn.to_q, hidden_states)
+                _lin(self.to_kv, hidden_states, out=own.view(b * l, -1))
             slots = list(self.buffer_list)
             self.comm_manager.enqueue(self.idx, own)
+        else:
+            if fusable:
+                q, kv = qkv_project(self, attn.to_q, self.to_kv, hidden_states)
+            else:
+                q, kv = _lin(attn.to_q, hidden_states), _lin(self.to_kv, hidden_states)
+            if n == 1:
+                slots = [kv]
+            elif self.buffer_list is None:
+                # no staging buffers yet: own K/V stands in for every strip (attn.py:132-133)
+                slots = [kv] * n
+            else:
+                dist.all_gather(self.buffer_list, kv, group=cfg.batch_group, async_op=False)
+                slots = list(self.buffer_list)
         o = ops.attention(q, slots, attn.heads)
         return _finish(attn, o, hidden_states, residual)
 

@@ -67,6 +67,27 @@ def linear(x, weight, bias=None, residual=None):
     return y.view(*lead, weight.shape[0])
 
 
+def gemm_dual(a, w, n1: int, bias=None, out1=None, out2=None):
+    """``a @ w^T (+ bias)`` with the first ``n1`` output columns written to ``out1`` and the
+    rest to ``out2`` (each with its own row stride)."""
+    _f16_cuda(a, "a"), _f16_cuda(w, "w")
+    M, K = a.shape
+    N = w.shape[0]
+    _req(w.shape[1] == K and a.stride(1) == 1 and w.stride(1) == 1, "gemm_dual: bad operands")
+    if out1 is None:
+        out1 = torch.empty((M, n1), device=a.device, dtype=torch.float16)
+    if out2 is None:
+        out2 = torch.empty((M, N - n1), device=a.device, dtype=torch.float16)
+    _req(out1.shape == (M, n1) and out2.shape == (M, N - n1) and out1.stride(1) == 1 and out2.stride(1) == 1, "gemm_dual: bad outputs")
+    l = _lib.lib()
+    _lib.check(
+        l.bxl_gemm_dual_f16(_p(a), a.stride(0), _p(w), w.stride(0), _p(bias), _p(out1), out1.stride(0), n1, _p(out2),
+                            out2.stride(0), M, N, K, _stream()),
+        l,
+    )
+    return out1, out2
+
+
 def geglu_interleave(weight: torch.Tensor, bias: torch.Tensor | None):
     """Reorder the rows of a GEGLU projection ([2F, K]: F value rows then F gate rows) into
     groups of 16 value rows followed by their 16 gate rows, the order ``gemm_geglu`` expects."""

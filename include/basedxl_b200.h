@@ -65,6 +65,15 @@ int bxl_gemm_f16(const void* A, long long lda, const void* B, long long ldb, int
                  const void* residual, long long ldr, void* C, long long ldc, int out_f32, int M, int N, int K,
                  void* stream);
 
+/* One projection, two destinations: [C1 | C2] = A[M,K] * B[N,K]^T + bias[N], the first n1
+ * output columns to C1 (row stride ldc1), the remaining N - n1 to C2 (row stride ldc2).
+ * n1 must be a multiple of 32.  Used for the fused q | k | v projection of self-attention:
+ * q goes to a scratch matrix, k|v straight into this strip's K/V staging slot.
+ * Replaces: to_q and to_kv of BasedXLSelfAttentionPP._forward (basedxl/modules/attn.py:123,127)
+ * and the staging copy of enqueue (basedxl/utils.py:156). */
+int bxl_gemm_dual_f16(const void* A, long long lda, const void* B, long long ldb, const void* bias, void* C1,
+                      long long ldc1, int n1, void* C2, long long ldc2, int M, int N, int K, void* stream);
+
 /* Feed-forward input projection with the GEGLU gate fused into the epilogue:
  * h = A[M,K] * B[N,K]^T + bias[N]; out[m, 16c+i] = h[m, 32c+i] * gelu(h[m, 32c+16+i]), i < 16.
  * B and bias are given with their rows INTERLEAVED in groups of 16 value rows followed by

@@ -36,6 +36,20 @@ def gemm(a, b, bias=None, residual=None, out=None, b_is_kn=False, out_f32=False)
     return y
 
 
+def gemm_dual(a, w, n1, bias=None, out1=None, out2=None):
+    y = a @ w.t()
+    if bias is not None:
+        y = y + bias
+    y1, y2 = y[:, :n1].contiguous(), y[:, n1:].contiguous()
+    if out1 is not None:
+        out1.copy_(y1)
+        y1 = out1
+    if out2 is not None:
+        out2.copy_(y2)
+        y2 = out2
+    return y1, y2
+
+
 def gemm_geglu(a, w_interleaved, bias_interleaved=None, out=None):
     h = a @ w_interleaved.t()
     if bias_interleaved is not None:
@@ -131,6 +145,6 @@ def install():
     """Replace the kernel wrappers of ``basedxl_b200.ops`` by the functions above."""
     from basedxl_b200 import ops
 
-    for name in ("gemm", "gemm_geglu", "conv_weight_pack", "conv3x3", "halo_pack", "groupnorm_stats", "groupnorm_apply", "attention",
+    for name in ("gemm", "gemm_dual", "gemm_geglu", "conv_weight_pack", "conv3x3", "halo_pack", "groupnorm_stats", "groupnorm_apply", "attention",
                  "upsample2x", "layernorm", "geglu"):
         setattr(ops, name, globals()[name])

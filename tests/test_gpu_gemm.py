@@ -169,3 +169,20 @@ def test_gemm_with_fused_geglu(M, K, F):
     _lib.device_status()
     assert y.shape == (M, F)
     assert_close(y, ref, what=f"gemm+geglu {M}x{K}x{F}")
+
+
+@pytest.mark.parametrize("M,K,C", [(300, 640, 640), (2048, 1280, 1280), (512, 128, 128)])
+def test_gemm_with_two_destinations(M, K, C):
+    """q | k|v projection in one launch, k|v into a wider (strided) destination."""
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    g = torch.Generator().manual_seed(M + C)
+    x = h16(torch.randn(M, K, generator=g))
+    w = h16(torch.randn(3 * C, K, generator=g) / K**0.5)
+    ref = x @ w.t()
+    slot = torch.zeros(M, 2 * C + 64, device=dev, dtype=torch.float16)
+    q, _ = ops.gemm_dual(x.half().to(dev), w.half().to(dev), C, out2=slot[:, : 2 * C])
+    _lib.device_status()
+    assert_close(q, ref[:, :C], what="q part")
+    assert_close(slot[:, : 2 * C], ref[:, C:], what="k|v part")
+    assert float(slot[:, 2 * C :].abs().max()) == 0.0
