@@ -49,6 +49,7 @@ struct alignas(64) GemmParams {
   // tiling chosen by the host
   int bn;                      // tile width: multiple of 32, 32..256
   int split;                   // K split over a cluster of `split` CTAs (1, 2 or 4)
+  int pair;                    // CTA pairs (cta_group::2): 256-row tiles, each CTA stages half of B (split == 1)
   int stages;                  // depth of the operand ring
   // epilogue
   const __half* bias;          // [N] or null
@@ -163,14 +164,16 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, float (&f)[32],
   }
 }
 
-template <bool kConv>
+template <bool kConv, bool kPair>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid_constant__ GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const int BN = p.bn;
-  const int S = p.split;
-  const int stage_bytes = kABytes + BN * 128;
+  const int S = kPair ? 1 : p.split;
+  const int b_rows = kPair ? BN / 2 : BN;       // rows of the B tile this CTA stages
+  const int stage_bytes = kABytes + b_rows * 128;
+  constexpr int kWidth = kPair ? 2 : 1;          // CTAs that cooperate on one tile (besides a K split)
   const uint32_t recv_base = smem_base + p.stages * stage_bytes;            // 1024-aligned (stage_bytes % 1024 == 0)
   const uint32_t bar_base = recv_base + recv_bytes(BN, S);
   // barriers (8 bytes each): full[kMaxStages], empty[kMaxStages], tfull[2], tempty[2], recv_full, recv_free
@@ -180,6 +183,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + 2 + a); };
   const uint32_t recv_full_bar = bar_base + 8u * (2 * kMaxStages + 4);
   const uint32_t recv_free_bar = bar_base + 8u * (2 * kMaxStages + 5);
+  // pair mode: the odd CTA reports "my half of stage s has landed" on the leader's pfull[s]
+  auto pfull_bar = [&](int s) { return bar_base + 8u * (2 * kMaxStages + 6 + s); };
   uint8_t* misc = smem_gen + (bar_base - smem_base) + 256;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 8);
@@ -188,16 +193,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t tmem_cols = (2 * BN <= 64) ? 64u : (2 * BN <= 128) ? 128u : (2 * BN <= 256) ? 256u : 512u;
-  const uint32_t crank = (S > 1) ? cluster_ctarank() : 0u;
+  const uint32_t crank = (S > 1 || kPair) ? cluster_ctarank() : 0u;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(full_bar(s), 2);   // one arrival (with its byte count) from each of the two producers
+      // one arrival (with its byte count) from each of this CTA's two producer threads
+      mbar_init(full_bar(s), 2);
       mbar_init(empty_bar(s), 1);
+      mbar_init(pfull_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+      mbar_init(tempty_bar(a), 4 * kWidth);  // one arrival per epilogue warp (of both CTAs in pair mode)
     }
     const uint32_t peers_threads = (S > 1) ? (S - 1) * 128u : 1u;  // every epilogue thread of every peer
     mbar_init(recv_full_bar, peers_threads);
@@ -206,29 +213,35 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), tmem_cols);
-    tmem_relinquish();
+    if (kPair) {
+      tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), tmem_cols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), tmem_cols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (S > 1) cluster_sync_all();  // peers' barriers are initialised before anyone arrives on them
+  if (S > 1 || kPair) cluster_sync_all();  // peers' barriers are initialised before anyone arrives on them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   pdl_wait();  // everything above overlaps the previous kernel's tail; global data from here on
 
   // ---- tile enumeration ------------------------------------------------------
   const int tiles_n = (p.N + BN - 1) / BN;
-  int tiles_m;
-  if (kConv) tiles_m = p.cB * p.tiles_y * p.tiles_x;
-  else tiles_m = (p.M + kBM - 1) / kBM;
+  int tiles_m1;  // 128-row tiles
+  if (kConv) tiles_m1 = p.cB * p.tiles_y * p.tiles_x;
+  else tiles_m1 = (p.M + kBM - 1) / kBM;
+  const int tiles_m = kPair ? (tiles_m1 + 1) / 2 : tiles_m1;  // scheduling units along M (pairs of tiles in pair mode)
   const int num_tiles = tiles_m * tiles_n;
   const int kb_per_seg = kConv ? 9 * (p.cCin / kBK) : (p.K + kBK - 1) / kBK;
   const int num_kb = kConv ? kb_per_seg : kb_per_seg * p.nseg;
   // this CTA's share of the K loop (balanced; never empty because split <= num_kb)
   const int kb_begin = static_cast<int>((static_cast<long long>(crank) * num_kb) / S);
   const int kb_end = static_cast<int>((static_cast<long long>(crank + 1) * num_kb) / S);
-  const int first_tile = blockIdx.x / S;
-  const int tile_step = gridDim.x / S;
+  const int first_tile = blockIdx.x / (S * kWidth);
+  const int tile_step = gridDim.x / (S * kWidth);
 
   if (warp == 0 || warp == 6) {
     // ======================= TMA producers =======================
@@ -243,11 +256,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
-        const int tm = tile % tiles_m;
+        const int tm = (tile % tiles_m) * kWidth + (kPair ? static_cast<int>(crank) : 0);  // this CTA's 128-row tile
         const int tn = tile / tiles_m;
-        const int n0 = tn * BN;
+        const int n0 = tn * BN + (kPair ? static_cast<int>(crank) * b_rows : 0);           // first B row this CTA stages
         int img = 0, y0 = 0, x0 = 0;
         if (kConv) {
+          // a pair's second tile may lie past the last image: its copies are then entirely out of
+          // bounds (zero fill) and its rows are not stored
           const int per_img = p.tiles_y * p.tiles_x;
           img = tm / per_img;
           const int r = tm % per_img;
@@ -261,8 +276,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
           }
           const uint32_t a_dst = smem_base + stage * stage_bytes;
           const uint32_t b_dst = a_dst + kABytes;
+          const uint32_t fbar = full_bar(stage);
           if (loads_a) {
-            mbar_arrive_expect_tx(full_bar(stage), kABytes);
+            mbar_arrive_expect_tx(fbar, kABytes);
             if (kConv) {
               const int cchunks = p.cCin / kBK;
               const int tap = kb / cchunks;
@@ -281,38 +297,33 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
               if (p.cStride == 1 && !touches_halo) {
                 // all th input rows come from the body (rows outside [0, H) are zero-filled by
                 // the copy engine): one copy for the whole A tile
-                tma_load_5d(a_dst, &p.a_rows_map, full_bar(stage), c0, par, x0 + xoff, r_first, img);
+                tma_load_5d(a_dst, &p.a_rows_map, fbar, c0, par, x0 + xoff, r_first, img);
               } else {
                 for (int t = 0; t < p.th; ++t) {
                   const int r_in = p.cStride * (y0 + t) + ky - 1;
                   const uint32_t dst = a_dst + t * p.tw * 128;
-                  if (r_in == -1 && p.has_top) {
-                    tma_load_5d(dst, &p.a_map[1], full_bar(stage), c0, par, x0 + xoff, 0, img);
-                  } else if (r_in == p.cHin && p.has_bot) {
-                    tma_load_5d(dst, &p.a_map[2], full_bar(stage), c0, par, x0 + xoff, 0, img);
-                  } else {
-                    tma_load_5d(dst, &p.a_map[0], full_bar(stage), c0, par, x0 + xoff, r_in, img);
-                  }
+                  const CUtensorMap* src = (r_in == -1 && p.has_top) ? &p.a_map[1] : (r_in == p.cHin && p.has_bot) ? &p.a_map[2] : &p.a_map[0];
+                  const int r_src = (src == &p.a_map[0]) ? r_in : 0;
+                  tma_load_5d(dst, src, fbar, c0, par, x0 + xoff, r_src, img);
                 }
               }
             } else {
               const int seg = kb / kb_per_seg;
               const int k0 = (kb % kb_per_seg) * kBK;
-              tma_load_2d(a_dst, &p.a_map[seg], full_bar(stage), k0, tm * kBM);
+              tma_load_2d(a_dst, &p.a_map[seg], fbar, k0, tm * kBM);
             }
           } else {
-            mbar_arrive_expect_tx(full_bar(stage), BN * 128);
+            mbar_arrive_expect_tx(fbar, b_rows * 128);
             if (kConv) {
-              tma_load_2d(b_dst, &p.b_map[0], full_bar(stage), kb * kBK, n0);
+              tma_load_2d(b_dst, &p.b_map[0], fbar, kb * kBK, n0);
             } else {
               const int seg = kb / kb_per_seg;
               const int k0 = (kb % kb_per_seg) * kBK;
               if (p.b_kn) {
                 // B[K,N]: one 64(n) x 64(k) box per 64 output columns
-                for (int j = 0; j < BN / 64; ++j)
-                  tma_load_2d(b_dst + j * 8192, &p.b_map[seg], full_bar(stage), n0 + j * 64, k0);
+                for (int j = 0; j < b_rows / 64; ++j) tma_load_2d(b_dst + j * 8192, &p.b_map[seg], fbar, n0 + j * 64, k0);
               } else {
-                tma_load_2d(b_dst, &p.b_map[seg], full_bar(stage), k0, n0);
+                tma_load_2d(b_dst, &p.b_map[seg], fbar, k0, n0);
               }
             }
           }
@@ -325,8 +336,28 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
     }
   } else if (warp == 1) {
     // ======================= MMA issuer =======================
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc_f16(kBM, BN, 0, (!kConv && p.b_kn) ? 1 : 0);
+    if (kPair && crank != 0) {
+      // odd CTA of a pair: report every landed stage to the leader, which issues the MMAs for both
+      if (lane == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+          for (int kb = kb_begin; kb < kb_end; ++kb) {
+            if (!mbar_wait(full_bar(stage), phase, abort_flag, p.dev_status, 210)) {
+              ok = false;
+              break;
+            }
+            mbar_arrive_remote(map_to_cta(pfull_bar(stage), 0));
+            if (++stage == p.stages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+      }
+    } else if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(kBM * kWidth, BN, 0, (!kConv && p.b_kn) ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -334,11 +365,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
       for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1u;
-        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.dev_status, 200)) break;
+        if (kPair ? !mbar_wait_cluster(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.dev_status, 200)
+                  : !mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.dev_status, 200))
+          break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.dev_status, 201)) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.dev_status, 201) ||
+              (kPair && !mbar_wait_cluster(pfull_bar(stage), phase, abort_flag, p.dev_status, 202))) {
             ok = false;
             break;
           }
@@ -351,21 +385,38 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
             // MN-major B: 64-column chunks 8 KB apart (LBO), 8-row k-groups 1 KB apart (SBO)
             const uint64_t bdesc = make_smem_desc_sw128(b_addr, 8192, 1024);
 #pragma unroll
-            for (int k = 0; k < kBK / kUmmaK; ++k)
-              umma_f16(d_tmem, adesc + 2u * k, bdesc + 128u * k, idesc, first | k);
+            for (int k = 0; k < kBK / kUmmaK; ++k) {
+              if (kPair) umma_f16_pair(d_tmem, adesc + 2u * k, bdesc + 128u * k, idesc, first | k);
+              else umma_f16(d_tmem, adesc + 2u * k, bdesc + 128u * k, idesc, first | k);
+            }
           } else {
             const uint64_t bdesc = make_smem_desc_sw128(b_addr, 16, 1024);
 #pragma unroll
-            for (int k = 0; k < kBK / kUmmaK; ++k)
-              umma_f16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, first | k);
+            for (int k = 0; k < kBK / kUmmaK; ++k) {
+              if (kPair) umma_f16_pair(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, first | k);
+              else umma_f16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, first | k);
+            }
           }
-          umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+          // frees the stage (in both CTAs of a pair) once these MMAs have read it
+          if (kPair) {
+            umma_commit_pair(empty_bar(stage));
+            umma_commit_pair(map_to_cta(empty_bar(stage), 1));
+          } else {
+            umma_commit(empty_bar(stage));
+          }
           if (++stage == p.stages) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) umma_commit(tfull_bar(acc));
+        if (ok) {
+          if (kPair) {
+            umma_commit_pair(tfull_bar(acc));
+            umma_commit_pair(map_to_cta(tfull_bar(acc), 1));
+          } else {
+            umma_commit(tfull_bar(acc));
+          }
+        }
       }
     }
   } else {
@@ -378,7 +429,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
     for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
-      const int tm = tile % tiles_m;
+      const int tm = (tile % tiles_m) * kWidth + (kPair ? static_cast<int>(crank) : 0);
       const int tn = tile / tiles_m;
       const int n0 = tn * BN;
       long long out_row = -1;  // row index into C / residual, -1 = not stored
@@ -389,7 +440,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
         const int r = tm % per_img;
         const int oy = (r / p.tiles_x) * p.th + row_in_tile / p.tw;
         const int ox = (r % p.tiles_x) * p.tw + row_in_tile % p.tw;
-        if (oy < p.cHout && ox < p.cWout) out_row = (static_cast<long long>(img) * p.cHout + oy) * p.cWout + ox;
+        if (img < p.cB && oy < p.cHout && ox < p.cWout) out_row = (static_cast<long long>(img) * p.cHout + oy) * p.cWout + ox;
       } else {
         const int m = tm * kBM + row_in_tile;
         if (m < p.M) out_row = m;
@@ -464,7 +515,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (lane == 0) {
+        if (kPair && crank != 0) mbar_arrive_remote(map_to_cta(tempty_bar(acc), 0));
+        else mbar_arrive(tempty_bar(acc));
+      }
     }
   }
 
@@ -479,11 +533,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
     __syncthreads();
   }
   // no CTA of a cluster may leave while a peer can still write into its shared memory
-  if (S > 1) cluster_sync_all();
+  if (S > 1 || kPair) cluster_sync_all();
   if (warp == 1) {
     __syncwarp();
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, tmem_cols);
+    if (kPair) tmem_dealloc_pair(tmem_base, tmem_cols);
+    else tmem_dealloc(tmem_base, tmem_cols);
   }
 }
 
@@ -491,74 +546,93 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
 // host side
 // ---------------------------------------------------------------------------------
 struct TileConfig {
-  int bn, split, stages;
+  int bn, split, stages, pair;
 };
 
-static int stages_for(int bn, int split) {
-  const int stage = kABytes + bn * 128;
+static int stages_for(int bn, int split, int pair = 0) {
+  const int stage = kABytes + (pair ? bn * 64 : bn * 128);
   int st = (kSmemBudget - kSmemMisc - recv_bytes(bn, split)) / stage;
   if (st > kMaxStages) st = kMaxStages;
   return st;
 }
 
-// Pick the tile width and the K split that minimise a time model calibrated on B200.
-// One CTA streams its operands at ~98 KB/us from L2 (the per-SM fill rate is what
-// bounds these kernels, not the tensor pipe), so a k-block of a 128 x bn tile costs
-// max(mma(bn), (16 KB + bn*128 B) / 98 KB/us); a wider tile moves fewer bytes per FLOP,
-// a narrower one or a K split spreads the stream over more SMs when there are few tiles.
-static TileConfig choose_tiles(int tiles_m, int N, int num_kb, bool b_kn, int force_bn = 0, int force_split = 0) {
+// Pick the tile width, the K split and whether to pair CTAs, minimising a time model
+// calibrated on B200.  One CTA streams its operands at ~98 KB/us from L2 (the per-SM fill
+// rate is what bounds these kernels, not the tensor pipe), so a k-block of a 128 x bn tile
+// costs max(mma(bn), bytes / 98 KB/us) with bytes = 16 KB + bn*128 B, or 16 KB + bn*64 B when
+// two CTAs share the B tile.  A wider tile or a CTA pair moves fewer bytes per FLOP; a
+// narrower tile or a K split spreads the stream over more SMs when there are few tiles.
+static TileConfig choose_tiles(int tiles_m, int N, int num_kb, bool b_kn, int force_bn = 0, int force_split = 0,
+                               int force_pair = -1) {
   const int sms = sm_count();
-  TileConfig best{128, 1, stages_for(128, 1)};
+  TileConfig best{128, 1, stages_for(128, 1), 0};
   double best_cost = 1e30;
-  for (int bn = 32; bn <= 256; bn += 32) {
-    if (b_kn && bn % 64) continue;            // MN-major B is loaded in 64-column boxes
-    if (force_bn && bn != force_bn) continue;
-    const int tiles = tiles_m * ((N + bn - 1) / bn);
-    for (int split = 1; split <= 4; split *= 2) {
-      if (force_split && split != force_split) continue;
-      if ((bn / 32) % split || split > num_kb) continue;
-      const int st = stages_for(bn, split);
-      if (st < 3) continue;
-      const int clusters = sms / split;
-      const int par = tiles < clusters ? tiles : clusters;
-      const int rounds = (tiles + par - 1) / par;
-      const double kb_us = fmax(bn / 256.0 * 0.27, (16384.0 + bn * 128.0) / 98000.0);
-      const double kb_unit = (num_kb + split - 1) / split;
-      const double epi_us = 0.12 * (bn / 32.0) / split + (split > 1 ? 1.2 : 0.0);   // accumulator read-out (+ exchange)
-      const double fill_us = 1.0 + (st < 4 ? 0.5 : 0.0);                             // pipeline ramp per unit
-      const double cost = rounds * (kb_unit * kb_us + epi_us) + fill_us + 3.0;
-      if (cost < best_cost - 1e-9) {
-        best_cost = cost;
-        best = TileConfig{bn, split, st};
+  for (int pair = 0; pair <= 1; ++pair) {
+    if (force_pair >= 0 && pair != force_pair) continue;
+    for (int bn = 32; bn <= 256; bn += 32) {
+      if (b_kn && (pair ? bn % 128 : bn % 64)) continue;  // MN-major B is loaded in 64-column boxes
+      if (force_bn && bn != force_bn) continue;
+      const int units_m = pair ? (tiles_m + 1) / 2 : tiles_m;
+      const int tiles = units_m * ((N + bn - 1) / bn);
+      for (int split = 1; split <= (pair ? 1 : 4); split *= 2) {
+        if (force_split && split != force_split) continue;
+        if ((bn / 32) % split || split > num_kb) continue;
+        const int st = stages_for(bn, split, pair);
+        if (st < 3) continue;
+        const int width = pair ? 2 : split;
+        const int clusters = sms / width;
+        const int par = tiles < clusters ? tiles : clusters;
+        const int rounds = (tiles + par - 1) / par;
+        const double bytes = 16384.0 + bn * (pair ? 64.0 : 128.0);
+        const double kb_us = fmax(bn / 256.0 * 0.27, bytes / 98000.0);
+        const double kb_unit = (num_kb + split - 1) / split;
+        const double epi_us = 0.12 * (bn / 32.0) / split + (split > 1 ? 1.2 : 0.0);  // accumulator read-out (+ exchange)
+        const double fill_us = 1.0 + (st < 4 ? 0.5 : 0.0) + (pair ? 0.3 : 0.0);       // pipeline ramp per unit
+        const double cost = rounds * (kb_unit * kb_us + epi_us) + fill_us + 3.0;
+        if (cost < best_cost - 1e-9) {
+          best_cost = cost;
+          best = TileConfig{bn, split, st, pair};
+        }
       }
     }
   }
   return best;
 }
 
-template <bool kConv>
-static int launch(const GemmParams& p, int num_tiles, cudaStream_t stream) {
-  const int smem = p.stages * (kABytes + p.bn * 128) + recv_bytes(p.bn, p.split) + kSmemMisc;
+template <bool kConv, bool kPair>
+static int launch_one(const GemmParams& p, int num_units, cudaStream_t stream) {
+  const int b_rows = kPair ? p.bn / 2 : p.bn;
+  const int smem = p.stages * (kABytes + b_rows * 128) + recv_bytes(p.bn, kPair ? 1 : p.split) + kSmemMisc;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    if (int rc = check_cuda(cudaFuncSetAttribute(gemm_conv_kernel<kConv>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget),
+    if (int rc = check_cuda(cudaFuncSetAttribute(gemm_conv_kernel<kConv, kPair>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget),
                             "cudaFuncSetAttribute(gemm)"))
       return rc;
     configured[dev] = true;
   }
-  int clusters = sm_count() / p.split;
-  if (clusters > num_tiles) clusters = num_tiles;
+  const int width = kPair ? 2 : p.split;
+  int clusters = sm_count() / width;
+  if (clusters > num_units) clusters = num_units;
   if (clusters < 1) clusters = 1;
-  return launch_kernel("gemm_conv_kernel launch", gemm_conv_kernel<kConv>, dim3(clusters * p.split), dim3(kGemmThreads), smem,
-                       stream, p.split, p);
+  return launch_kernel("gemm_conv_kernel launch", gemm_conv_kernel<kConv, kPair>, dim3(clusters * width), dim3(kGemmThreads), smem,
+                       stream, width, p);
+}
+
+// tiles_m: 128-row tiles along M; tiles_n: tiles along N
+template <bool kConv>
+static int launch(const GemmParams& p, int tiles_m, int tiles_n, cudaStream_t stream) {
+  if (p.pair) return launch_one<kConv, true>(p, ((tiles_m + 1) / 2) * tiles_n, stream);
+  return launch_one<kConv, false>(p, tiles_m * tiles_n, stream);
 }
 
 static int aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // test hook: force the tile width / K split (0 = choose)
-static int g_force_bn = 0, g_force_split = 0;
+// CTA pairing stays off unless asked for until the model below is trusted to choose it
+constexpr int kDefaultPair = 0;  // -1 = let the cost model decide
+static int g_force_bn = 0, g_force_split = 0, g_force_pair = -1;
 
 }  // namespace bxl
 
@@ -580,7 +654,7 @@ extern "C" int bxl_gemm_f16(const void* A, long long lda, const void* B, long lo
   GemmParams p;
   memset(&p, 0, sizeof(p));
   const int tiles_m = (M + kBM - 1) / kBM;
-  const TileConfig tc = choose_tiles(tiles_m, N, (K + kBK - 1) / kBK, b_is_kn != 0, g_force_bn, g_force_split);
+  const TileConfig tc = choose_tiles(tiles_m, N, (K + kBK - 1) / kBK, b_is_kn != 0, g_force_bn, g_force_split, g_force_pair < 0 ? kDefaultPair : g_force_pair);
   const int BN = tc.bn;
   {
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
@@ -596,7 +670,7 @@ extern "C" int bxl_gemm_f16(const void* A, long long lda, const void* B, long lo
   } else {
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
     uint64_t str[1] = {(uint64_t)ldb * 2};
-    uint32_t box[2] = {kBK, (uint32_t)BN};
+    uint32_t box[2] = {kBK, (uint32_t)(tc.pair ? BN / 2 : BN)};
     if (int rc = encode_tmap_f16(&p.b_map[0], B, 2, dims, str, box)) return rc;
   }
   for (int s = 1; s < kMaxSeg; ++s) {
@@ -604,13 +678,12 @@ extern "C" int bxl_gemm_f16(const void* A, long long lda, const void* B, long lo
     p.b_map[s] = p.b_map[0];
   }
   p.M = M, p.N = N, p.K = K, p.nseg = 1, p.b_kn = b_is_kn ? 1 : 0;
-  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages;
+  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair;
   p.bias = static_cast<const __half*>(bias);
   p.residual = static_cast<const __half*>(residual);
   p.ldr = ldr, p.C = C, p.ldc = ldc, p.out_f32 = out_f32 ? 1 : 0;
   p.dev_status = st;
-  const int tiles = tiles_m * ((N + BN - 1) / BN);
-  return launch<false>(p, tiles, (cudaStream_t)stream);
+  return launch<false>(p, tiles_m, (N + BN - 1) / BN, (cudaStream_t)stream);
 }
 
 extern "C" int bxl_gemm_dual_f16(const void* A, long long lda, const void* B, long long ldb, const void* bias, void* C1,
@@ -627,7 +700,7 @@ extern "C" int bxl_gemm_dual_f16(const void* A, long long lda, const void* B, lo
   GemmParams p;
   memset(&p, 0, sizeof(p));
   const int tiles_m = (M + kBM - 1) / kBM;
-  const TileConfig tc = choose_tiles(tiles_m, N, (K + kBK - 1) / kBK, false, g_force_bn, g_force_split);
+  const TileConfig tc = choose_tiles(tiles_m, N, (K + kBK - 1) / kBK, false, g_force_bn, g_force_split, g_force_pair < 0 ? kDefaultPair : g_force_pair);
   {
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
     uint64_t str[1] = {(uint64_t)lda * 2};
@@ -637,7 +710,7 @@ extern "C" int bxl_gemm_dual_f16(const void* A, long long lda, const void* B, lo
   {
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
     uint64_t str[1] = {(uint64_t)ldb * 2};
-    uint32_t box[2] = {kBK, (uint32_t)tc.bn};
+    uint32_t box[2] = {kBK, (uint32_t)(tc.pair ? tc.bn / 2 : tc.bn)};
     if (int rc = encode_tmap_f16(&p.b_map[0], B, 2, dims, str, box)) return rc;
   }
   for (int s = 1; s < kMaxSeg; ++s) {
@@ -645,11 +718,11 @@ extern "C" int bxl_gemm_dual_f16(const void* A, long long lda, const void* B, lo
     p.b_map[s] = p.b_map[0];
   }
   p.M = M, p.N = N, p.K = K, p.nseg = 1, p.b_kn = 0;
-  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages;
+  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair;
   p.bias = static_cast<const __half*>(bias);
   p.C = C1, p.ldc = ldc1, p.C2 = C2, p.ldc2 = ldc2, p.n_split = n1;
   p.dev_status = st;
-  return launch<false>(p, tiles_m * ((N + tc.bn - 1) / tc.bn), (cudaStream_t)stream);
+  return launch<false>(p, tiles_m, (N + tc.bn - 1) / tc.bn, (cudaStream_t)stream);
 }
 
 extern "C" int bxl_gemm_geglu_f16(const void* A, long long lda, const void* B, long long ldb, const void* bias, void* C,
@@ -664,7 +737,7 @@ extern "C" int bxl_gemm_geglu_f16(const void* A, long long lda, const void* B, l
   GemmParams p;
   memset(&p, 0, sizeof(p));
   const int tiles_m = (M + kBM - 1) / kBM;
-  const TileConfig tc = choose_tiles(tiles_m, N, (K + kBK - 1) / kBK, false, g_force_bn, g_force_split);
+  const TileConfig tc = choose_tiles(tiles_m, N, (K + kBK - 1) / kBK, false, g_force_bn, g_force_split, g_force_pair < 0 ? kDefaultPair : g_force_pair);
   {
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
     uint64_t str[1] = {(uint64_t)lda * 2};
@@ -674,7 +747,7 @@ extern "C" int bxl_gemm_geglu_f16(const void* A, long long lda, const void* B, l
   {
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
     uint64_t str[1] = {(uint64_t)ldb * 2};
-    uint32_t box[2] = {kBK, (uint32_t)tc.bn};
+    uint32_t box[2] = {kBK, (uint32_t)(tc.pair ? tc.bn / 2 : tc.bn)};
     if (int rc = encode_tmap_f16(&p.b_map[0], B, 2, dims, str, box)) return rc;
   }
   for (int s = 1; s < kMaxSeg; ++s) {
@@ -682,17 +755,17 @@ extern "C" int bxl_gemm_geglu_f16(const void* A, long long lda, const void* B, l
     p.b_map[s] = p.b_map[0];
   }
   p.M = M, p.N = N, p.K = K, p.nseg = 1, p.b_kn = 0;
-  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages;
+  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair;
   p.bias = static_cast<const __half*>(bias);
   p.C = C, p.ldc = ldc, p.out_f32 = 0, p.geglu = 1;
   p.dev_status = st;
-  return launch<false>(p, tiles_m * ((N + tc.bn - 1) / tc.bn), (cudaStream_t)stream);
+  return launch<false>(p, tiles_m, (N + tc.bn - 1) / tc.bn, (cudaStream_t)stream);
 }
 
-extern "C" int bxl_debug_force_tiles(int bn, int split) {
-  if (bn < 0 || bn > 256 || bn % 32 || (split != 0 && split != 1 && split != 2 && split != 4))
-    return fail(kErrInvalidArg, "bxl_debug_force_tiles: bn must be 0 or a multiple of 32 up to 256, split 0, 1, 2 or 4");
-  g_force_bn = bn, g_force_split = split;
+extern "C" int bxl_debug_force_tiles(int bn, int split, int pair) {
+  if (bn < 0 || bn > 256 || bn % 32 || (split != 0 && split != 1 && split != 2 && split != 4) || pair < -1 || pair > 1)
+    return fail(kErrInvalidArg, "bxl_debug_force_tiles: bn must be 0 or a multiple of 32 up to 256, split 0, 1, 2 or 4, pair -1, 0 or 1");
+  g_force_bn = bn, g_force_split = split, g_force_pair = pair;
   return kOk;
 }
 
@@ -742,7 +815,7 @@ extern "C" int bxl_gemm_split_f32(const float* A, const float* B, float* C, int 
   GemmParams p;
   memset(&p, 0, sizeof(p));
   const int tiles_m = (M + kBM - 1) / kBM;
-  const TileConfig tc = choose_tiles(tiles_m, N, 3 * ((K + kBK - 1) / kBK), true, g_force_bn, g_force_split);
+  const TileConfig tc = choose_tiles(tiles_m, N, 3 * ((K + kBK - 1) / kBK), true, g_force_bn, g_force_split, g_force_pair < 0 ? kDefaultPair : g_force_pair);
   const int BN = tc.bn;
   // C = A_hi*B_hi + A_hi*B_lo + A_lo*B_hi, one fp32 accumulator
   const __half* as[3] = {a_hi, a_hi, a_lo};
@@ -758,11 +831,10 @@ extern "C" int bxl_gemm_split_f32(const float* A, const float* B, float* C, int 
     if (int rc = encode_tmap_f16(&p.b_map[i], bs[i], 2, bd, bstr, bbox)) return rc;
   }
   p.M = M, p.N = N, p.K = K, p.nseg = 3, p.b_kn = 1;
-  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages;
+  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair;
   p.C = C, p.ldc = N, p.out_f32 = 1;
   p.dev_status = st;
-  const int tiles = tiles_m * ((N + BN - 1) / BN);
-  return launch<false>(p, tiles, s);
+  return launch<false>(p, tiles_m, (N + BN - 1) / BN, s);
 }
 
 // ---- convolution --------------------------------------------------------------------
@@ -829,18 +901,18 @@ extern "C" int bxl_conv3x3_halo_f16(const void* x, long long x_img_stride, const
   if (int rc = enc(&p.a_map[2], bot ? bot : x, 1, bot ? halo_img_stride : x_img_stride)) return rc;
   const int K = 9 * C_in;
   const int tiles_x = (W_out + tw - 1) / tw, tiles_y = (H_out + th - 1) / th;
-  const TileConfig tc = choose_tiles(B * tiles_x * tiles_y, C_out, K / kBK, false, g_force_bn, g_force_split);
+  const TileConfig tc = choose_tiles(B * tiles_x * tiles_y, C_out, K / kBK, false, g_force_bn, g_force_split, g_force_pair < 0 ? kDefaultPair : g_force_pair);
   const int BN = tc.bn;
   {
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)C_out};
     uint64_t str[1] = {(uint64_t)K * 2};
-    uint32_t box[2] = {kBK, (uint32_t)BN};
+    uint32_t box[2] = {kBK, (uint32_t)(tc.pair ? BN / 2 : BN)};
     if (int rc = encode_tmap_f16(&p.b_map[0], w_packed, 2, dims, str, box)) return rc;
   }
   p.b_map[1] = p.b_map[0];
   p.b_map[2] = p.b_map[0];
   p.M = B * H_out * W_out, p.N = C_out, p.K = K, p.nseg = 1, p.b_kn = 0;
-  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages;
+  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair;
   p.bias = static_cast<const __half*>(bias);
   p.bias_rows = static_cast<const __half*>(bias_rows);
   p.residual = static_cast<const __half*>(residual);
@@ -850,6 +922,5 @@ extern "C" int bxl_conv3x3_halo_f16(const void* x, long long x_img_stride, const
   p.tiles_x = tiles_x, p.tiles_y = tiles_y;
   p.has_top = top ? 1 : 0, p.has_bot = bot ? 1 : 0;
   p.dev_status = st;
-  const int tiles = B * tiles_x * tiles_y * ((C_out + BN - 1) / BN);
-  return launch<true>(p, tiles, (cudaStream_t)stream);
+  return launch<true>(p, B * tiles_x * tiles_y, (C_out + BN - 1) / BN, (cudaStream_t)stream);
 }

@@ -44,15 +44,15 @@ def main():
     ap.add_argument("kernel", choices=["gemm", "conv", "attention", "groupnorm", "geglu", "layernorm"])
     for n, d in [("M", 2048), ("K", 1280), ("N", 1280), ("B", 2), ("Cin", 640), ("Cout", 640), ("C", 1280), ("H", 64), ("W", 64),
                  ("heads", 10), ("Lq", 4096), ("Lslot", 4096), ("slots", 1), ("stride", 1), ("iters", 10), ("warmup", 3),
-                 ("bn", 0), ("split", 0)]:
+                 ("bn", 0), ("split", 0), ("pair", -1)]:
         ap.add_argument(f"--{n}", type=int, default=d)
     ap.add_argument("--no-flush", action="store_true")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
     l = _lib.lib()
-    if a.bn or a.split:
-        _lib.check(l.bxl_debug_force_tiles(a.bn, a.split), l, kernels=0)
+    if a.bn or a.split or a.pair >= 0:
+        _lib.check(l.bxl_debug_force_tiles(a.bn, a.split, a.pair), l, kernels=0)
     g = torch.Generator(device="cuda").manual_seed(0)
     rn = lambda *s: torch.randn(*s, device=dev, generator=g).half()
     if a.kernel == "gemm":

@@ -45,10 +45,10 @@ int bxl_sm_count(void);
  * the environment, or this call with 0, turns it off.  No counterpart in the reference. */
 int bxl_set_pdl(int enabled);
 
-/* Test hook: force the GEMM / convolution tile width (multiple of 32, <= 256) and
- * K split (1, 2 or 4); 0 restores the built-in choice.  No counterpart in the
- * reference. */
-int bxl_debug_force_tiles(int bn, int split);
+/* Test hook: force the GEMM / convolution tile width (multiple of 32, <= 256), the K
+ * split (1, 2 or 4) and CTA pairing (1 = 256-row tiles on two CTAs, 0 = off); 0 / 0 / -1
+ * restore the built-in choice.  No counterpart in the reference. */
+int bxl_debug_force_tiles(int bn, int split, int pair);
 
 /* ---- matmul ------------------------------------------------------------- */
 

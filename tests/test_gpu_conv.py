@@ -180,7 +180,7 @@ def test_conv_forced_tile_width_and_k_split(bn, split):
     xs, xps = torch.chunk(x, 2, 2), torch.chunk(xp, 2, 2)
     stale = [po.conv2d_boundary(t, 1) for t in xps]
     l = _lib.lib()
-    _lib.check(l.bxl_debug_force_tiles(bn, split), l, kernels=0)
+    _lib.check(l.bxl_debug_force_tiles(bn, split, -1), l, kernels=0)
     try:
         for i in range(2):
             ref = po.conv2d_pp(xs[i], w, b, 1, 1, stale, i, 2)
@@ -189,7 +189,7 @@ def test_conv_forced_tile_width_and_k_split(bn, split):
             _lib.device_status()
             assert_close(y, ref, what=f"conv bn={bn} split={split} strip {i}")
     finally:
-        _lib.check(l.bxl_debug_force_tiles(0, 0), l, kernels=0)
+        _lib.check(l.bxl_debug_force_tiles(0, 0, -1), l, kernels=0)
 
 
 @pytest.mark.parametrize("n", [1, 2, 4, 8])

@@ -124,13 +124,13 @@ def test_forced_tile_width_and_k_split(M, K, N, b_is_kn, bn, split):
     bias, res = torch.randn(N, generator=g), torch.randn(M, N, generator=g)
     ref = h16(a) @ h16(w).t() + h16(bias) + h16(res)
     l = _lib.lib()
-    _lib.check(l.bxl_debug_force_tiles(bn, split), l, kernels=0)
+    _lib.check(l.bxl_debug_force_tiles(bn, split, -1), l, kernels=0)
     try:
         y = ops.gemm(a.half().to(dev), (w.t().contiguous() if b_is_kn else w).half().to(dev), bias=bias.half().to(dev),
                      residual=res.half().to(dev), b_is_kn=b_is_kn)
         _lib.device_status()
     finally:
-        _lib.check(l.bxl_debug_force_tiles(0, 0), l, kernels=0)
+        _lib.check(l.bxl_debug_force_tiles(0, 0, -1), l, kernels=0)
     assert_close(y, ref, what=f"gemm bn={bn} split={split}")
 
 
@@ -186,3 +186,25 @@ def test_gemm_with_two_destinations(M, K, C):
     assert_close(q, ref[:, :C], what="q part")
     assert_close(slot[:, : 2 * C], ref[:, C:], what="k|v part")
     assert float(slot[:, 2 * C :].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("M,K,N", [(300, 320, 384), (2048, 1280, 1280)])
+def test_cta_pair_tiles(M, K, N, bn):
+    """256-row tiles computed by two CTAs with one MMA stream (cta_group::2), each CTA staging
+    half of the B tile.  Not selected by default; kept correct for the shapes it may serve."""
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    g = torch.Generator().manual_seed(M + bn)
+    a = torch.randn(M, K, generator=g)
+    w = torch.randn(N, K, generator=g) / K**0.5
+    bias = torch.randn(N, generator=g)
+    ref = h16(a) @ h16(w).t() + h16(bias)
+    l = _lib.lib()
+    _lib.check(l.bxl_debug_force_tiles(bn, 1, 1), l, kernels=0)
+    try:
+        y = ops.gemm(a.half().to(dev), w.half().to(dev), bias=bias.half().to(dev))
+        _lib.device_status()
+    finally:
+        _lib.check(l.bxl_debug_force_tiles(0, 0, -1), l, kernels=0)
+    assert_close(y, ref, what=f"pair gemm bn={bn}")
