@@ -25,6 +25,17 @@ constexpr int kGnMaxParts = 128;   // per-image partial slabs
 constexpr int kGnMaxGroups = 64;
 constexpr int kGnMaxC = 4096;
 
+__device__ __forceinline__ void accumulate8(const uint4 u, float (&s1)[8], float (&s2)[8]) {
+  const __half2 h[4] = {*reinterpret_cast<const __half2*>(&u.x), *reinterpret_cast<const __half2*>(&u.y),
+                        *reinterpret_cast<const __half2*>(&u.z), *reinterpret_cast<const __half2*>(&u.w)};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __half22float2(h[j]);
+    s1[2 * j] += f.x, s2[2 * j] = fmaf(f.x, f.x, s2[2 * j]);
+    s1[2 * j + 1] += f.y, s2[2 * j + 1] = fmaf(f.y, f.y, s2[2 * j + 1]);
+  }
+}
+
 // scratch layout: [0] ticket counter (int, kept at 0 between launches), then
 // partials [B][parts][G][2] floats starting at byte 256
 __global__ void __launch_bounds__(512) groupnorm_stats_kernel(const __half* __restrict__ x, long long img_stride, int HW,
@@ -47,16 +58,17 @@ __global__ void __launch_bounds__(512) groupnorm_stats_kernel(const __half* __re
     const int per = (HW + parts - 1) / parts;
     const int p0 = part * per, p1 = min(HW, p0 + per);
     const __half* base = x + (long long)img * img_stride + (long long)v * 8;
-    for (int pix = p0 + r; pix < p1; pix += rows) {
-      const uint4 u = *reinterpret_cast<const uint4*>(base + (long long)pix * C);
-      const __half2* h = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __half22float2(h[j]);
-        s1[2 * j] += f.x, s2[2 * j] += f.x * f.x;
-        s1[2 * j + 1] += f.y, s2[2 * j + 1] += f.y * f.y;
-      }
+    auto accumulate = [&](const uint4 u) { accumulate8(u, s1, s2); };
+    int pix = p0 + r;
+    // four pixels per trip: four independent 16-byte loads in flight per thread
+    for (; pix + 3 * rows < p1; pix += 4 * rows) {
+      const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(base + (long long)pix * C));
+      const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(base + (long long)(pix + rows) * C));
+      const uint4 u2 = __ldg(reinterpret_cast<const uint4*>(base + (long long)(pix + 2 * rows) * C));
+      const uint4 u3 = __ldg(reinterpret_cast<const uint4*>(base + (long long)(pix + 3 * rows) * C));
+      accumulate(u0), accumulate(u1), accumulate(u2), accumulate(u3);
     }
+    for (; pix < p1; pix += rows) accumulate(__ldg(reinterpret_cast<const uint4*>(base + (long long)pix * C)));
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       atomicAdd(&s_ch[v * 8 + j], s1[j]);
@@ -97,6 +109,12 @@ __global__ void __launch_bounds__(512) groupnorm_stats_kernel(const __half* __re
     // published layout [2][B][G]: first moments, then second moments
     if (lane == 0) moments[((long long)which * B + b) * G + g] = acc * inv_n;
   }
+}
+
+__device__ __forceinline__ float fast_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 struct GnPeers {
@@ -172,8 +190,9 @@ __global__ void __launch_bounds__(512) groupnorm_apply_kernel(const __half* __re
       float y0 = f.x * a[2 * j] + b[2 * j];
       float y1 = f.y * a[2 * j + 1] + b[2 * j + 1];
       if (silu) {
-        y0 = y0 / (1.f + __expf(-y0));
-        y1 = y1 / (1.f + __expf(-y1));
+        // y * sigmoid(y) with sigmoid(y) = 0.5 * tanh(0.5 y) + 0.5: one special-function op per value
+        y0 = y0 * fmaf(0.5f, fast_tanh(0.5f * y0), 0.5f);
+        y1 = y1 * fmaf(0.5f, fast_tanh(0.5f * y1), 0.5f);
       }
       oh[j] = __floats2half2_rn(y0, y1);
     }
@@ -190,8 +209,8 @@ static int gn_threads(int C) {
 
 static int gn_parts(int HW, int C, int B) {
   const int rows = gn_threads(C) / (C / 8);
-  int parts = (HW + rows * 4 - 1) / (rows * 4);  // >= 4 sweeps per CTA
-  const int cap = max(1, (sm_count() * 4) / max(1, B));
+  int parts = (HW + rows * 16 - 1) / (rows * 16);  // >= 16 pixels per thread: the per-CTA fold is amortised
+  const int cap = max(1, (sm_count() * 2) / max(1, B));
   if (parts > cap) parts = cap;
   if (parts > kGnMaxParts) parts = kGnMaxParts;
   if (parts < 1) parts = 1;
