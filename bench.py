@@ -39,7 +39,11 @@ import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
 IMAGE_STEPS = 50
-METRIC = "sdxl_1024_50step_unet_s_per_image"
+METRIC = "sdxl_1024_50step_unet_s_per_image"  # the name carries the configured resolution, see metric_name()
+
+
+def metric_name(height: int) -> str:
+    return f"sdxl_{height}_50step_unet_s_per_image"
 UNIT = "s/image"
 
 
@@ -160,7 +164,11 @@ def gemm_kernel_roofline(device, n_strips: int, height: int, width: int, peaks) 
     return {
         "bound": "tensor", "kernel": "gemm_conv_kernel (linear layers)", "achieved": round(achieved, 1),
         "peak": peaks["tflops_burst"], "peak_kind": f"{peaks['source']} burst (kernel timed alone)", "unit": "TFLOP/s",
-        "frac": round(achieved / peaks["tflops_burst"], 4), "traffic": None, "per_shape": per_shape,
+        "frac": round(achieved / peaks["tflops_burst"], 4),
+        # dram__bytes_read + dram__bytes_write of one launch of this kernel under ncu (profiles/gemm_8192x2560x5120.md):
+        # 76.4 + 61.2 MB for M=8192 K=2560 N=5120, whose algorithmic bytes are 68 MB read + 84 MB written
+        "traffic": {"bytes_per_launch": 137.6e6, "case": "M=8192 K=2560 N=5120", "algorithmic_bytes": 151.9e6},
+        "per_shape": per_shape,
     }
 
 
@@ -216,7 +224,7 @@ def run_reference_arm(args):
     sample = (f"per step: one UNet forward, CFG batch 2, {sample_hw}x{sample_hw} latent, fp32, stock PyTorch CPU operators; "
               f"extrapolated to the {full_hw}x{full_hw} latent by algorithmic FLOPs (x{ratio:.1f}) and to {IMAGE_STEPS} steps")
     line = {
-        "impl": "reference", "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "impl": "reference", "metric": metric_name(args.height), "value": round(value, 2), "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(per_step * ratio * 1e3, 1), "higher_is_better": False, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"SDXL {args.height}x{args.width} UNet loop, 50 Euler steps, CFG batch 2 (CPU path of the reference: PyTorch modules on host cores)"},
@@ -318,7 +326,7 @@ def run_b200_arm(args):
     if rank == 0:
         par = "1 gpu" if world == 1 else (f"cfg2 x {n_strips} strips" if n_strips > 1 else "cfg2")
         line = {
-            "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "metric": metric_name(args.height), "value": round(value, 4), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms_per_step, 3), "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"SDXL {args.height}x{args.width} UNet loop: latent 1x4x{args.height // 8}x{args.width // 8}, CFG batch 2, guidance 5.0, 50 Euler steps, 5 synchronous steps then displaced",
