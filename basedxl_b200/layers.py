@@ -97,6 +97,18 @@ class Attention(nn.Module):
             self._kv = (key, fuse_kv(self.to_k, self.to_v))
         return self._kv[1]
 
+    def _project_kv(self, ctx: torch.Tensor, out=None) -> torch.Tensor:
+        """K|V of ``ctx`` as one ``[B, L, 2C]`` tensor.  With stock Linear projections this is one
+        GEMM on the stacked weight; with swapped-in replacements the two projections are called
+        as they are and their results laid side by side."""
+        if isinstance(self.to_k, nn.Linear):
+            return _lin(self._fused_kv(), ctx, out=out)
+        kv = torch.cat([_lin(self.to_k, ctx), _lin(self.to_v, ctx)], dim=-1)
+        if out is not None:
+            out.copy_(kv.reshape(out.shape))
+            return out.view(*ctx.shape[:-1], kv.shape[-1])
+        return kv
+
     def context_kv(self, ctx: torch.Tensor, force: bool = False) -> torch.Tensor:
         """K/V projection of the conditioning, computed when the conditioning tensor changes
         (new storage or a new version) and otherwise reused: it is the same for all denoising
@@ -106,9 +118,9 @@ class Attention(nn.Module):
         key = (ctx.data_ptr(), ctx._version, tuple(ctx.shape))
         b, l, _ = ctx.shape
         if self._ctx_kv is None or self._ctx_kv.shape[:2] != (b, l):
-            self._ctx_kv = _lin(self._fused_kv(), ctx)
+            self._ctx_kv = self._project_kv(ctx)
         elif force or key != self._ctx_key:
-            _lin(self._fused_kv(), ctx, out=self._ctx_kv.view(b * l, -1))
+            self._project_kv(ctx, out=self._ctx_kv.view(b * l, -1))
         self._ctx_key = key
         self._ctx_ref = ctx  # keeps the storage alive, so its address cannot be reused by another tensor
         return self._ctx_kv
@@ -118,7 +130,7 @@ class Attention(nn.Module):
             if type(self.to_q) is Linear and self.to_q.out_features % 32 == 0:
                 q, kv = qkv_project(self, self.to_q, self._fused_kv(), hidden_states)
             else:
-                q, kv = _lin(self.to_q, hidden_states), _lin(self._fused_kv(), hidden_states)
+                q, kv = _lin(self.to_q, hidden_states), self._project_kv(hidden_states)
         else:
             q = _lin(self.to_q, hidden_states)
             kv = self.context_kv(encoder_hidden_states)

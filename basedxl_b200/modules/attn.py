@@ -69,7 +69,16 @@ def qkv_project(owner, to_q: nn.Linear, to_kv: nn.Linear, x: torch.Tensor, kv_ou
     return q.view(*lead, c), kv.view(*lead, 2 * c) if kv_out is None else None
 
 
-def _lin(layer: nn.Linear, x: torch.Tensor, residual=None, out=None) -> torch.Tensor:
+def _lin(layer: nn.Module, x: torch.Tensor, residual=None, out=None) -> torch.Tensor:
+    if not isinstance(layer, nn.Linear):
+        # a swapped-in replacement (e.g. BasedXLLowPLinear, which keeps its weight as [K, N])
+        y = layer(x, residual=residual) if getattr(layer, "supports_fused_epilogue", False) else layer(x)
+        if residual is not None and not getattr(layer, "supports_fused_epilogue", False):
+            y = y + residual
+        if out is not None:
+            out.copy_(y.reshape(out.shape))
+            return out.view(*x.shape[:-1], out.shape[-1])
+        return y
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1])
     r2 = None if residual is None else residual.reshape(-1, layer.out_features)

@@ -65,3 +65,27 @@ def test_sdxl_unet_forward_matches_oracle_at_reduced_resolution():
     from basedxl_b200.sdxl_unet import sdxl_config
 
     _compare(sdxl_config(), 32, 2e-3, "SDXL UNet forward, 32x32 latent")
+
+
+def test_tiny_unet_with_lowp_linear_swap_matches_oracle():
+    """``fp16_acc_matmul=True``: every Linear replaced by BasedXLLowPLinear (weights kept as
+    [K, N]), as the reference's patch_linear_layers does (basedxl/unet.py:81-87)."""
+    dev = cuda_or_skip()
+    from basedxl_b200 import _lib
+    from basedxl_b200.modules.lowp_linear import BasedXLLowPLinear
+    from basedxl_b200.sdxl_unet import tiny_config
+    from basedxl_b200.unet import BasedXLUnet
+    from basedxl_b200.utils import BasedXLConfig
+
+    cfg = tiny_config()
+    ref, gpu = _pair(cfg, dev)
+    wrapped = BasedXLUnet(gpu, BasedXLConfig(fp16_acc_matmul=True))
+    assert any(isinstance(m, BasedXLLowPLinear) for m in gpu.modules())
+    x, ehs, added = _inputs(cfg, 32)
+    with torch.no_grad():
+        y_ref = ref(x, torch.tensor(999.0), ehs, added_cond_kwargs=added)[0]
+        y = wrapped(x.to(dev), torch.tensor(999.0, device=dev), ehs.half().to(dev),
+                    added_cond_kwargs={k: v.to(dev) for k, v in added.items()})[0]
+    _lib.device_status()
+    err = rel_l2(y.float().cpu(), y_ref)
+    assert err <= 2e-3, err
