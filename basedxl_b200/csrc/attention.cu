@@ -53,6 +53,7 @@ struct alignas(64) AttnParams {
   __half* out;                     // [B, L_q, ld_out]
   long long out_img_stride, ld_out;
   float scale_log2e;               // softmax scale * log2(e)
+  int kv_split;                    // K/V range split over a cluster of 1, 2 or 4 CTAs
   int* dev_status;
 };
 
@@ -126,14 +127,26 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
   // S_0 [0,128) S_1 [128,256) O_0 [256,320) O_1 [320,384) L_0 [384,400) L_1 [400,416)
   constexpr uint32_t kTmemCols = 512;
 
+  // With kv_split = S > 1 the S CTAs of a cluster serve the same 256 queries, each over 1/S of
+  // the K/V tiles; their partial (max, sum, output) triples are merged through distributed
+  // shared memory at the end (every CTA merges 256/S of the rows).
+  const int S = p.kv_split;
+  const uint32_t crank = (S > 1) ? cluster_ctarank() : 0u;
+  const int work = blockIdx.x / S;
   const int q_pairs = (p.L_q + 2 * kTileQ - 1) / (2 * kTileQ);
-  const int qp = blockIdx.x % q_pairs;
-  const int head = (blockIdx.x / q_pairs) % p.heads;
-  const int img = blockIdx.x / (q_pairs * p.heads);
+  const int qp = work % q_pairs;
+  const int head = (work / q_pairs) % p.heads;
+  const int img = work / (q_pairs * p.heads);
   const int q_row0 = qp * 2 * kTileQ;
   const int n_groups = (q_row0 + kTileQ < p.L_q) ? 2 : 1;   // the second tile may lie wholly past L_q
   const int tiles_per_slot = (p.L_slot + kTileKV - 1) / kTileKV;
-  const int n_tiles = p.n_slots * tiles_per_slot;
+  const int total_tiles = p.n_slots * tiles_per_slot;
+  const int tile0 = static_cast<int>((static_cast<long long>(crank) * total_tiles) / S);   // first K/V tile of this CTA
+  const int n_tiles = static_cast<int>((static_cast<long long>(crank + 1) * total_tiles) / S) - tile0;
+  // per-thread result of the K/V loop (softmax threads), kept across the final hand-over
+  uint32_t fin_o[kHeadDim];
+  float fin_l = 0.f, fin_m = -INFINITY;
+  bool fin_valid = false;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -174,8 +187,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
       int stage = 0;
       uint32_t phase = 0;
       for (int j = 0; j < n_tiles; ++j) {
-        const int slot = j / tiles_per_slot;
-        const int t0 = (j % tiles_per_slot) * kTileKV;
+        const int slot = (tile0 + j) / tiles_per_slot;
+        const int t0 = ((tile0 + j) % tiles_per_slot) * kTileKV;
         if (!mbar_wait(kv_empty(stage), phase ^ 1u, abort_flag, p.dev_status, 400)) break;
         mbar_arrive_expect_tx(kv_full(stage), 32768);
         tma_load_3d(smem_base + AttnSmem::kK + stage * 16384, &p.kv_map[slot], kv_full(stage), head * kHeadDim, t0, img);
@@ -275,7 +288,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
       constexpr float kRaise = 8.f;  // raise m only when the tile maximum exceeds it by 2^8
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int t0 = (j % tiles_per_slot) * kTileKV;
+        const int t0 = ((tile0 + j) % tiles_per_slot) * kTileKV;
         const int valid = min(kTileKV, p.L_slot - t0);
         if (!mbar_wait(s_full(g), j & 1u, abort_flag, p.dev_status, 600)) {
           ok = false;
@@ -385,30 +398,74 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
           tmem_ld_32x32(o_addr + 32, o1);
           const uint32_t lp = tmem_ld_1(l_addr);
           tmem_ld_wait();
-          const int q_row = q_row0 + g * kTileQ + row;
-          if (q_row < p.L_q) {
-            const float inv_l = 1.f / __uint_as_float(lp);
-            __half* dst = p.out + (long long)img * p.out_img_stride + (long long)q_row * p.ld_out + head * kHeadDim;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 u;
-              __half2* h = reinterpret_cast<__half2*>(&u);
-#pragma unroll
-              for (int i = 0; i < 4; ++i)
-                h[i] = __floats2half2_rn(__uint_as_float(o0[q * 8 + 2 * i]) * inv_l, __uint_as_float(o0[q * 8 + 2 * i + 1]) * inv_l);
-              *reinterpret_cast<uint4*>(dst + q * 8) = u;
-            }
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 u;
-              __half2* h = reinterpret_cast<__half2*>(&u);
-#pragma unroll
-              for (int i = 0; i < 4; ++i)
-                h[i] = __floats2half2_rn(__uint_as_float(o1[q * 8 + 2 * i]) * inv_l, __uint_as_float(o1[q * 8 + 2 * i + 1]) * inv_l);
-              *reinterpret_cast<uint4*>(dst + 32 + q * 8) = u;
-            }
-          }
+          for (int i = 0; i < 32; ++i) fin_o[i] = o0[i], fin_o[32 + i] = o1[i];
+          fin_l = __uint_as_float(lp);
+          fin_m = m_run;
+          fin_valid = true;
         }
+      }
+    }
+  }
+
+  // ---- hand-over: merge the K/V splits (if any) and write the output ----------------
+  tc_fence_before_sync();
+  __syncthreads();
+  const bool softmax_thread = (warp >= 2) && (((warp - 2) >> 2) < n_groups);
+  const int sg = (warp - 2) >> 2, srow = (warp & 3) * 32 + lane;     // group and row of a softmax thread
+  const int grow = sg * kTileQ + srow;                                 // row within the CTA's 256 queries
+  if (S > 1) {
+    // every CTA of the cluster has left its K/V loop: the K/V ring of each CTA is free and serves
+    // as the receive buffer  [sender][66 values][rows owned] (fp32)
+    cluster_sync_all();
+    const int rows_owned = 2 * kTileQ / S;
+    const uint32_t owner = softmax_thread ? static_cast<uint32_t>(grow / rows_owned) : 0u;
+    const int lrow = grow % rows_owned;
+    const uint32_t recv = smem_base + AttnSmem::kK;
+    if (softmax_thread && owner != crank && fin_valid) {
+      const uint32_t slot = (crank < owner) ? crank : crank - 1;
+      const uint32_t base = map_to_cta(recv + ((slot * 66u) * rows_owned + lrow) * 4u, owner);
+      const uint32_t stride = rows_owned * 4u;
+#pragma unroll
+      for (int i = 0; i < kHeadDim; ++i) st_cluster_f32(base + i * stride, __uint_as_float(fin_o[i]));
+      st_cluster_f32(base + 64u * stride, fin_l);
+      st_cluster_f32(base + 65u * stride, fin_m);
+    }
+    cluster_sync_all();  // all partials have landed
+    if (softmax_thread && owner == crank && fin_valid) {
+      const float* rbuf = reinterpret_cast<const float*>(smem_gen + AttnSmem::kK);
+      float m_all = fin_m;
+      for (int s2 = 0; s2 < S - 1; ++s2) m_all = fmaxf(m_all, rbuf[(s2 * 66 + 65) * rows_owned + lrow]);
+      const float own_scale = fast_exp2(fin_m - m_all);
+      float l_all = fin_l * own_scale;
+      float acc[kHeadDim];
+#pragma unroll
+      for (int i = 0; i < kHeadDim; ++i) acc[i] = __uint_as_float(fin_o[i]) * own_scale;
+      for (int s2 = 0; s2 < S - 1; ++s2) {
+        const float* rb = rbuf + (s2 * 66) * rows_owned + lrow;
+        const float sc2 = fast_exp2(rb[65 * rows_owned] - m_all);
+        l_all = fmaf(rb[64 * rows_owned], sc2, l_all);
+#pragma unroll
+        for (int i = 0; i < kHeadDim; ++i) acc[i] = fmaf(rb[i * rows_owned], sc2, acc[i]);
+      }
+      fin_l = l_all;
+#pragma unroll
+      for (int i = 0; i < kHeadDim; ++i) fin_o[i] = __float_as_uint(acc[i]);
+    }
+  }
+  if (softmax_thread && fin_valid && (S == 1 || static_cast<uint32_t>(grow / (2 * kTileQ / S)) == crank)) {
+    const int q_row = q_row0 + grow;
+    if (q_row < p.L_q) {
+      const float inv_l = 1.f / fin_l;
+      __half* dst = p.out + (long long)img * p.out_img_stride + (long long)q_row * p.ld_out + head * kHeadDim;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        uint4 u;
+        __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          h[i] = __floats2half2_rn(__uint_as_float(fin_o[q * 8 + 2 * i]) * inv_l, __uint_as_float(fin_o[q * 8 + 2 * i + 1]) * inv_l);
+        *reinterpret_cast<uint4*>(dst + q * 8) = u;
       }
     }
   }
@@ -428,9 +485,17 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
   }
 }
 
+static int g_force_attn_split = 0;  // test hook: 0 = choose
+
 }  // namespace bxl
 
 using namespace bxl;
+
+extern "C" int bxl_debug_force_attn_split(int split) {
+  if (split != 0 && split != 1 && split != 2 && split != 4) return fail(kErrInvalidArg, "bxl_debug_force_attn_split: 0, 1, 2 or 4");
+  g_force_attn_split = split;
+  return kOk;
+}
 
 extern "C" int bxl_attn_fwd_f16(const void* q, long long q_img_stride, long long ld_q, const void* const* kv_slots,
                                 int n_slots, long long kv_img_stride, long long ld_kv, int v_col0, void* out,
@@ -478,6 +543,20 @@ extern "C" int bxl_attn_fwd_f16(const void* q, long long q_img_stride, long long
     configured[dev] = true;
   }
   const int q_pairs = (L_q + 2 * kTileQ - 1) / (2 * kTileQ);
-  return launch_kernel("attention_kernel launch", attention_kernel, dim3(q_pairs * heads * B), dim3(kAttnThreads),
-                       AttnSmem::kTotal, (cudaStream_t)stream, 1, p);
+  const int work = q_pairs * heads * B;
+  const int total_tiles = n_slots * ((L_slot + kTileKV - 1) / kTileKV);
+  // K/V split: fewest rounds x tiles per round, with a fixed per-CTA cost of ~2.5 tiles and
+  // ~1.5 tiles for the merge
+  int split = 1;
+  double best = 1e30;
+  for (int s2 = 1; s2 <= 4; s2 *= 2) {
+    if (s2 > total_tiles || (g_force_attn_split && s2 != g_force_attn_split)) continue;
+    const int clusters = sm_count() / s2;
+    const int rounds = (work + clusters - 1) / clusters;
+    const double cost = rounds * ((total_tiles + s2 - 1) / s2 + 2.5 + (s2 > 1 ? 1.5 : 0.0));
+    if (cost < best - 1e-9) best = cost, split = s2;
+  }
+  p.kv_split = split;
+  return launch_kernel("attention_kernel launch", attention_kernel, dim3(work * split), dim3(kAttnThreads), AttnSmem::kTotal,
+                       (cudaStream_t)stream, split, p);
 }

@@ -111,6 +111,9 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 __device__ __forceinline__ void st_cluster_f32x4(uint32_t cluster_addr, float a, float b, float c, float d) {
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
+__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float a) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(a) : "memory");
+}
 // Arrive on an mbarrier of another CTA of the cluster; orders this thread's
 // earlier (remote) stores before the arrival.
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {

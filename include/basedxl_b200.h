@@ -50,6 +50,10 @@ int bxl_set_pdl(int enabled);
  * restore the built-in choice.  No counterpart in the reference. */
 int bxl_debug_force_tiles(int bn, int split, int pair);
 
+/* Test hook: force the K/V split of the attention kernel (1, 2 or 4 CTAs per query block;
+ * 0 restores the built-in choice).  No counterpart in the reference. */
+int bxl_debug_force_attn_split(int split);
+
 /* ---- matmul ------------------------------------------------------------- */
 
 /* C[M,N] = A[M,K] * B (+ bias[N]) (+ residual[M,N]); fp16 operands, fp32

@@ -113,3 +113,27 @@ def test_benchmark_shape_self_attention():
         y = ops.attention(q[:, i * ls : (i + 1) * ls].half().to(dev), [s.half().to(dev).contiguous() for s in slots], heads)
         _lib.device_status()
         assert_close(y, ref, what=f"self-attention n={n}")
+
+
+@pytest.mark.parametrize("split", [1, 2, 4])
+@pytest.mark.parametrize("B,heads,Lq,Lslot,nslots", [(1, 2, 256, 128, 4), (2, 3, 200, 72, 5), (1, 20, 256, 256, 4), (2, 10, 512, 77, 1), (1, 4, 640, 512, 2)])
+def test_attention_kv_split_over_a_cluster(B, heads, Lq, Lslot, nslots, split):
+    """The K/V range split over 1, 2 or 4 CTAs per query block and merged through distributed
+    shared memory gives the same result (ragged tiles, several slots, odd query-tile counts)."""
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    if split > nslots * ((Lslot + 127) // 128):
+        pytest.skip("more splits than key/value tiles")
+    C = heads * 64
+    gen = torch.Generator().manual_seed(B + heads + Lq + Lslot + nslots)
+    q = h16(torch.randn(B, Lq, C, generator=gen))
+    slots = [h16(torch.randn(B, Lslot, 2 * C, generator=gen) * (1.0 + 2.0 * i)) for i in range(nslots)]  # very different maxima per slot
+    ref = po._sdpa_heads(q, torch.cat(slots, dim=1), heads)
+    l = _lib.lib()
+    _lib.check(l.bxl_debug_force_attn_split(split), l, kernels=0)
+    try:
+        y = ops.attention(q.half().to(dev), [s.half().to(dev) for s in slots], heads)
+        _lib.device_status()
+    finally:
+        _lib.check(l.bxl_debug_force_attn_split(0), l, kernels=0)
+    assert_close(y, ref, tol=3e-3, what=f"attention split={split}")
