@@ -40,6 +40,7 @@ SIGNATURES = {
     "bxl_upsample2x_f16": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
     "bxl_layernorm_f16": (_i, [_vp, _vp, _vp, _vp, _ll, _i, _f, _vp]),
     "bxl_geglu_f16": (_i, [_vp, _vp, _ll, _i, _vp]),
+    "bxl_cfg_euler_step": (_i, [_vp, _vp, _vp, _ll, _f, _f, _f, _vp]),
 }
 
 

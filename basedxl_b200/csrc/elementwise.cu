@@ -259,6 +259,24 @@ __global__ void geglu_kernel(const __half* __restrict__ h, __half* __restrict__ 
   }
 }
 
+// ---- guidance combine + Euler update + input scaling for the next step -------------------
+// eps [2][n] fp16 (row 0 unconditional, row 1 conditional); latents [n] fp32 updated in place;
+// next_input [2][n] fp16 = latents / sqrt(sigma_next^2 + 1), the same in both rows.
+__global__ void cfg_euler_kernel(const __half* __restrict__ eps, float* __restrict__ latents, __half* __restrict__ next_input,
+                                 long long n, float guidance, float dsigma, float in_scale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float e0 = __half2float(eps[i]), e1 = __half2float(eps[n + i]);
+    const float e = e0 + guidance * (e1 - e0);
+    const float x = latents[i] + e * dsigma;
+    latents[i] = x;
+    const __half h = __float2half_rn(x * in_scale);
+    next_input[i] = h;
+    next_input[n + i] = h;
+  }
+}
+
 static int grid_for(long long work_items, int threads) {
   long long blocks = (work_items + threads - 1) / threads;
   const long long cap = (long long)sm_count() * 16;
@@ -345,4 +363,13 @@ extern "C" int bxl_geglu_f16(const void* h, void* out, long long rows, int F, vo
   if (!h || !out || rows <= 0 || F <= 0 || F % 8 || !al16(h) || !al16(out)) return fail(kErrInvalidArg, "bxl_geglu_f16: bad argument");
   return launch_kernel("geglu_kernel launch", geglu_kernel, dim3(grid_for(rows * (F / 8), 256)), dim3(256), 0, (cudaStream_t)stream, 1,
                        static_cast<const __half*>(h), static_cast<__half*>(out), rows, F);
+}
+
+extern "C" int bxl_cfg_euler_step(const void* eps, float* latents, void* next_input, long long n, float guidance, float sigma,
+                                  float sigma_next, void* stream) {
+  if (!eps || !latents || !next_input || n <= 0) return fail(kErrInvalidArg, "bxl_cfg_euler_step: bad argument");
+  const float in_scale = 1.f / sqrtf(sigma_next * sigma_next + 1.f);
+  return launch_kernel("cfg_euler_kernel launch", cfg_euler_kernel, dim3(grid_for(n, 256)), dim3(256), 0, (cudaStream_t)stream, 1,
+                       static_cast<const __half*>(eps), latents, static_cast<__half*>(next_input), n, guidance,
+                       sigma_next - sigma, in_scale);
 }

@@ -85,12 +85,24 @@ class BasedXLPipeline:
         if first_step == 0 and scale_initial:
             latents = latents * sch.init_noise_sigma
         last_step = num_inference_steps if last_step is None else last_step
+        fused = latents.is_cuda and dt == torch.float16 and latents.shape[0] == 1
+        if fused:
+            from . import ops
+
+            latents = latents.contiguous().clone()  # updated in place by the fused step
+            x2 = torch.empty((2, *latents.shape[1:]), device=latents.device, dtype=dt)
+            x = sch.scale_model_input(latents, first_step).to(dt)
+            x2[0:1], x2[1:2] = x, x
         for i in range(first_step, last_step):
-            x = sch.scale_model_input(latents, i).to(dt)
-            x2 = torch.cat([x, x])
-            eps = self.unet(x2, sch.timesteps[i], ehs, added_cond_kwargs=added)[0].float()
-            eps = eps[0:1] + guidance_scale * (eps[1:2] - eps[0:1])
-            latents = sch.step(eps, i, latents)
+            if fused:
+                eps = self.unet(x2, sch.timesteps[i], ehs, added_cond_kwargs=added)[0]
+                # guidance + Euler update + scaling of the next input: one kernel
+                ops.cfg_euler_step(eps.contiguous(), latents, x2, guidance_scale, sch.sigmas[i], sch.sigmas[i + 1])
+            else:
+                x = sch.scale_model_input(latents, i).to(dt)
+                eps = self.unet(torch.cat([x, x]), sch.timesteps[i], ehs, added_cond_kwargs=added)[0].float()
+                eps = eps[0:1] + guidance_scale * (eps[1:2] - eps[0:1])
+                latents = sch.step(eps, i, latents)
         return latents
 
     @torch.no_grad()

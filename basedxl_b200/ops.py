@@ -317,3 +317,16 @@ def geglu(h):
     l = _lib.lib()
     _lib.check(l.bxl_geglu_f16(_p(h), _p(out), h.numel() // (2 * F), F, _stream()), l)
     return out
+
+
+def cfg_euler_step(eps, latents, next_input, guidance: float, sigma: float, sigma_next: float):
+    """Guidance combine, Euler update of ``latents`` (fp32, in place) and the scaled fp16 input
+    of the next step (both CFG rows) in one launch."""
+    _f16_cuda(eps, "eps"), _f16_cuda(next_input, "next_input")
+    _req(latents.is_cuda and latents.dtype == torch.float32 and latents.is_contiguous(), "cfg_euler_step: fp32 contiguous latents")
+    n = latents.numel()
+    _req(eps.is_contiguous() and next_input.is_contiguous() and eps.numel() == 2 * n and next_input.numel() == 2 * n,
+         "cfg_euler_step: eps and next_input must be contiguous [2, ...] tensors matching the latents")
+    l = _lib.lib()
+    _lib.check(l.bxl_cfg_euler_step(_p(eps), _p(latents), _p(next_input), n, float(guidance), float(sigma), float(sigma_next), _stream()), l)
+    return latents, next_input

@@ -190,6 +190,15 @@ int bxl_layernorm_f16(const void* x, void* y, const void* gamma, const void* bet
 /* out[rows,F] = h[:, :F] * gelu(h[:, F:]) for h[rows,2F] (exact erf GELU). */
 int bxl_geglu_f16(const void* h, void* out, long long rows, int F, void* stream);
 
+/* One kernel for what follows the UNet in every denoising step: classifier-free guidance
+ * eps = eps_u + g (eps_c - eps_u) on eps[2][n] (fp16), the Euler update
+ * latents += eps * (sigma_next - sigma) in fp32 (in place), and the next model input
+ * next_input[2][n] = latents / sqrt(sigma_next^2 + 1) (fp16, both CFG rows).
+ * Replaces: the guidance combine and scheduler step the denoising loop runs around
+ * BasedXLUnet.forward (the loop of basedxl/model.py:39-45 / sample.py:68-75). */
+int bxl_cfg_euler_step(const void* eps, float* latents, void* next_input, long long n, float guidance, float sigma,
+                       float sigma_next, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

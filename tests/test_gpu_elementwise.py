@@ -43,3 +43,22 @@ def test_geglu():
     a, g = h.chunk(2, dim=-1)
     assert_close(y, a * F.gelu(g), what="geglu")
     _lib.device_status()
+
+
+def test_cfg_euler_step():
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    g = torch.Generator().manual_seed(0)
+    eps = torch.randn(2, 4, 32, 32, generator=g).half()
+    lat = torch.randn(1, 4, 32, 32, generator=g) * 10
+    guidance, s0, s1 = 5.0, 3.2, 2.9
+    e = eps[0:1].float() + guidance * (eps[1:2].float() - eps[0:1].float())
+    ref_lat = lat + e * (s1 - s0)
+    ref_in = (ref_lat / (s1 * s1 + 1) ** 0.5).half()
+    lat_d = lat.to(dev).clone()
+    nxt = torch.empty(2, 4, 32, 32, device=dev, dtype=torch.float16)
+    ops.cfg_euler_step(eps.to(dev), lat_d, nxt, guidance, s0, s1)
+    _lib.device_status()
+    assert torch.allclose(lat_d.cpu(), ref_lat, rtol=1e-6, atol=1e-5)
+    assert torch.equal(nxt[0].cpu(), nxt[1].cpu())
+    assert (nxt[0:1].float().cpu() - ref_in.float()).abs().max() <= 2e-2
