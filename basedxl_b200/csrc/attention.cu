@@ -40,7 +40,7 @@ constexpr int kAttnThreads = 320;
 constexpr int kHeadDim = 64;
 constexpr int kTileQ = 128;
 constexpr int kTileKV = 128;
-constexpr int kKvStages = 3;
+constexpr int kKvStages = 4;
 constexpr int kMaxSlots = 8;
 
 struct alignas(64) AttnParams {
@@ -61,9 +61,7 @@ struct AttnSmem {
   static constexpr int kQ = 0;                               // 2 x 16 KB
   static constexpr int kK = 32768;                           // kKvStages x 16 KB
   static constexpr int kV = kK + kKvStages * 16384;          // kKvStages x 16 KB
-  static constexpr int kP = kV + kKvStages * 16384;          // 2 groups x 2 halves x 16 KB
-  static constexpr int kOnes = kP + 65536;                   // 16 rows x 128 fp16 of 1.0 (two 2 KB halves): row-sum operand
-  static constexpr int kBar = kOnes + 4096;
+  static constexpr int kBar = kV + kKvStages * 16384;
   static constexpr int kTotal = kBar + 1024 + 1024;
 };
 
@@ -72,12 +70,10 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// two exponentials per MUFU operation: exp2 of a packed pair of fp16 arguments
-__device__ __forceinline__ uint32_t exp2_f16x2(float a, float b) {
-  uint32_t packed, y;
-  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(b), "f"(a));  // low half = a, high half = b
-  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(packed));
-  return y;
+__device__ __forceinline__ uint32_t pack_f16x2(float a, float b) {
+  uint32_t packed;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(b), "f"(a));
+  return packed;
 }
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
@@ -95,16 +91,7 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
       "r"(r[31])
       : "memory");
 }
-__device__ __forceinline__ void tmem_st_1(uint32_t taddr, uint32_t v) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(v) : "memory");
-}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ uint32_t tmem_ld_1(uint32_t taddr) {
-  uint32_t r;
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
-  return r;
-}
-
 __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -124,7 +111,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  // S_0 [0,128) S_1 [128,256) O_0 [256,320) O_1 [320,384) L_0 [384,400) L_1 [400,416)
+  // S_0 [0,128) S_1 [128,256) O_0 [256,320) O_1 [320,384) P_0 [384,448) P_1 [448,512)
+  // (P: 128 fp16 per row packed two per 32-bit column, the A operand of the P V product)
   constexpr uint32_t kTmemCols = 512;
 
   // With kv_split = S > 1 the S CTAs of a cluster serve the same 256 queries, each over 1/S of
@@ -167,10 +155,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
     tmem_relinquish();
   }
-  // constant operand of the row-sum product: every element 1.0 (layout-agnostic)
-  for (int i = threadIdx.x; i < 4096 / 4; i += blockDim.x)
-    reinterpret_cast<uint32_t*>(smem_gen + AttnSmem::kOnes)[i] = 0x3C003C00u;
-  fence_proxy_async_smem();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -205,9 +189,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_f16(128, 128, 0, 0);  // S = Q K^T, both K-major
       const uint32_t idesc_o = make_idesc_f16(128, 64, 0, 1);   // O = P V, V MN-major
-      const uint32_t idesc_l = make_idesc_f16(128, 16, 0, 0);   // row sums: L = P 1 (16 identical columns)
-      const uint64_t ones0 = make_smem_desc_sw128(smem_base + AttnSmem::kOnes, 16, 1024);
-      const uint64_t ones1 = make_smem_desc_sw128(smem_base + AttnSmem::kOnes + 2048, 16, 1024);
       bool ok = mbar_wait(q_full, 0, abort_flag, p.dev_status, 500);
       auto issue_s = [&](int j, int g) {
         const int st = j % kKvStages;
@@ -243,29 +224,19 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
             tc_fence_after_sync();
             issue_s(j + 1, g);
           }
-          // P_g(j) is in shared memory; O_g and L_g carry the right scale
+          // P_g(j) is in tensor memory; O_g carries the right scale
           if (!mbar_wait(p_full(g), j & 1u, abort_flag, p.dev_status, 502)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint64_t pdesc0 = make_smem_desc_sw128(smem_base + AttnSmem::kP + g * 32768, 16, 1024);
-          const uint64_t pdesc1 = make_smem_desc_sw128(smem_base + AttnSmem::kP + g * 32768 + 16384, 16, 1024);
           const uint32_t d = tmem_base + 256 + g * 64;
-          const uint32_t dl = tmem_base + 384 + g * 16;
+          const uint32_t pt = tmem_base + 384 + g * 64;
           const uint32_t acc = (j != 0);
 #pragma unroll
           for (int k = 0; k < kTileKV / 16; ++k) {
-            // tokens 16k..16k+15: P columns are K-major (32 B per step inside a 64-column half),
-            // V rows advance by 16 x 128 B
-            const uint64_t pd = ((k < 4) ? pdesc0 : pdesc1) + 2u * (k & 3);
-            umma_f16(d, pd, vdesc + 128u * k, idesc_o, acc | k);
-          }
-          // row sums of the rounded P on the tensor core, exact in fp32
-#pragma unroll
-          for (int k = 0; k < kTileKV / 16; ++k) {
-            const uint64_t pd = ((k < 4) ? pdesc0 : pdesc1) + 2u * (k & 3);
-            umma_f16(dl, pd, ((k < 4) ? ones0 : ones1) + 2u * (k & 3), idesc_l, acc | k);
+            // tokens 16k..16k+15: 8 packed columns of P, V rows advance by 16 x 128 B
+            umma_f16_ts(d, pt + 8u * k, vdesc + 128u * k, idesc_o, acc | k);
           }
           umma_commit(o_full(g));
           if (g == n_groups - 1) umma_commit(kv_empty(st));  // K_j and V_j are no longer needed
@@ -281,9 +252,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
       const uint32_t s_addr = t_lane + g * 128;
       const uint32_t o_addr = t_lane + 256 + g * 64;
-      const uint32_t l_addr = t_lane + 384 + g * 16;
+      const uint32_t p_addr = t_lane + 384 + g * 64;
       float m_run = -INFINITY;   // running row maximum in the exp2 domain (score * scale * log2 e)
-      uint8_t* p_smem = smem_gen + AttnSmem::kP + g * 32768;
+      float l_run = 0.f;         // running row sum of P, same reference as O
       const float sc = p.scale_log2e;
       constexpr float kRaise = 8.f;  // raise m only when the tile maximum exceeds it by 2^8
       bool ok = true;
@@ -305,14 +276,20 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
         tmem_ld_wait();
         tc_fence_before_sync();
         mbar_arrive(s_free(g));
-        float m_tile = -INFINITY;
+        // row maximum over the valid columns
+        float m_tile;
         if (valid == kTileKV) {
+          float ma = -INFINITY, mb = -INFINITY, mc = -INFINITY, md = -INFINITY;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            m_tile = max3(m_tile, __uint_as_float(v0[i]), __uint_as_float(v1[i]));
-            m_tile = max3(m_tile, __uint_as_float(v2[i]), __uint_as_float(v3[i]));
+          for (int i = 0; i < 32; i += 2) {
+            ma = max3(ma, __uint_as_float(v0[i]), __uint_as_float(v0[i + 1]));
+            mb = max3(mb, __uint_as_float(v1[i]), __uint_as_float(v1[i + 1]));
+            mc = max3(mc, __uint_as_float(v2[i]), __uint_as_float(v2[i + 1]));
+            md = max3(md, __uint_as_float(v3[i]), __uint_as_float(v3[i + 1]));
           }
+          m_tile = fmaxf(fmaxf(ma, mb), fmaxf(mc, md));
         } else {
+          m_tile = -INFINITY;
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             if (i < valid) m_tile = fmaxf(m_tile, __uint_as_float(v0[i]));
@@ -330,25 +307,36 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
           m_run = m_new;
         }
         const bool rescale = __any_sync(0xffffffffu, alpha != 1.f);
-        // P = exp2(S*scale - m) as packed fp16
-        uint32_t pk[64];
+        // P = exp2(S*scale - m) in fp32, summed in fp32, packed to fp16 for the tensor core:
+        // pa = columns [0,64), pb = columns [64,128), two per 32-bit word
+        uint32_t pa[32], pb[32];
+        float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+        if (valid == kTileKV) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          pk[i] = exp2_f16x2(fmaf(__uint_as_float(v0[2 * i]), sc, -m_run), fmaf(__uint_as_float(v0[2 * i + 1]), sc, -m_run));
-          pk[16 + i] = exp2_f16x2(fmaf(__uint_as_float(v1[2 * i]), sc, -m_run), fmaf(__uint_as_float(v1[2 * i + 1]), sc, -m_run));
-          pk[32 + i] = exp2_f16x2(fmaf(__uint_as_float(v2[2 * i]), sc, -m_run), fmaf(__uint_as_float(v2[2 * i + 1]), sc, -m_run));
-          pk[48 + i] = exp2_f16x2(fmaf(__uint_as_float(v3[2 * i]), sc, -m_run), fmaf(__uint_as_float(v3[2 * i + 1]), sc, -m_run));
-        }
-        if (valid != kTileKV) {
+          for (int i = 0; i < 16; ++i) {
+            const float a0 = fast_exp2(fmaf(__uint_as_float(v0[2 * i]), sc, -m_run)), a1 = fast_exp2(fmaf(__uint_as_float(v0[2 * i + 1]), sc, -m_run));
+            const float b0 = fast_exp2(fmaf(__uint_as_float(v1[2 * i]), sc, -m_run)), b1 = fast_exp2(fmaf(__uint_as_float(v1[2 * i + 1]), sc, -m_run));
+            const float c0 = fast_exp2(fmaf(__uint_as_float(v2[2 * i]), sc, -m_run)), c1 = fast_exp2(fmaf(__uint_as_float(v2[2 * i + 1]), sc, -m_run));
+            const float d0 = fast_exp2(fmaf(__uint_as_float(v3[2 * i]), sc, -m_run)), d1 = fast_exp2(fmaf(__uint_as_float(v3[2 * i + 1]), sc, -m_run));
+            sum0 += a0 + a1, sum1 += b0 + b1, sum2 += c0 + c1, sum3 += d0 + d1;
+            pa[i] = pack_f16x2(a0, a1), pa[16 + i] = pack_f16x2(b0, b1), pb[i] = pack_f16x2(c0, c1), pb[16 + i] = pack_f16x2(d0, d1);
+          }
+        } else {
+          // ragged last tile of a slot: columns >= valid contribute nothing
+          auto pexp = [&](uint32_t sv, int col) { return (col < valid) ? fast_exp2(fmaf(__uint_as_float(sv), sc, -m_run)) : 0.f; };
 #pragma unroll
-          for (int i = 0; i < 64; ++i) {
-            const int col = 2 * i;
-            if (col >= valid) pk[i] = 0u;
-            else if (col + 1 >= valid) pk[i] &= 0x0000FFFFu;
+          for (int i = 0; i < 16; ++i) {
+            const float a0 = pexp(v0[2 * i], 2 * i), a1 = pexp(v0[2 * i + 1], 2 * i + 1);
+            const float b0 = pexp(v1[2 * i], 32 + 2 * i), b1 = pexp(v1[2 * i + 1], 33 + 2 * i);
+            const float c0 = pexp(v2[2 * i], 64 + 2 * i), c1 = pexp(v2[2 * i + 1], 65 + 2 * i);
+            const float d0 = pexp(v3[2 * i], 96 + 2 * i), d1 = pexp(v3[2 * i + 1], 97 + 2 * i);
+            sum0 += a0 + a1, sum1 += b0 + b1, sum2 += c0 + c1, sum3 += d0 + d1;
+            pa[i] = pack_f16x2(a0, a1), pa[16 + i] = pack_f16x2(b0, b1), pb[i] = pack_f16x2(c0, c1), pb[16 + i] = pack_f16x2(d0, d1);
           }
         }
-        // the previous tile's P V product must have finished: it read the P buffer, and O / L
-        // are only touched between two products
+        l_run = fmaf(l_run, alpha, (sum0 + sum1) + (sum2 + sum3));
+        // the previous tile's P V product must have finished: it read the P buffer, and O is only
+        // touched between two products
         if (j > 0) {
           if (!mbar_wait(o_full(g), (j - 1) & 1u, abort_flag, p.dev_status, 601)) {
             ok = false;
@@ -360,7 +348,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
             uint32_t o0[32], o1[32];
             tmem_ld_32x32(o_addr, o0);
             tmem_ld_32x32(o_addr + 32, o1);
-            const uint32_t lp = tmem_ld_1(l_addr);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
@@ -369,22 +356,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
             }
             tmem_st_32x32(o_addr, o0);
             tmem_st_32x32(o_addr + 32, o1);
-            tmem_st_1(l_addr, __float_as_uint(__uint_as_float(lp) * alpha));
-            tmem_st_wait();
           }
         }
-        // two 64-column halves of the P tile, 8 chunks of 16 B each
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          uint8_t* half_base = p_smem + hf * 16384;
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            *reinterpret_cast<uint4*>(half_base + sw128_offset(row, q)) =
-                make_uint4(pk[hf * 32 + 4 * q], pk[hf * 32 + 4 * q + 1], pk[hf * 32 + 4 * q + 2], pk[hf * 32 + 4 * q + 3]);
-          }
-        }
-        // publish P(j) (generic-proxy writes -> async proxy)
-        fence_proxy_async_smem();
+        // publish P(j) in tensor memory
+        tmem_st_32x32(p_addr, pa);
+        tmem_st_32x32(p_addr + 32, pb);
+        tmem_st_wait();
         tc_fence_before_sync();
         mbar_arrive(p_full(g));
       }
@@ -396,11 +373,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
           uint32_t o0[32], o1[32];
           tmem_ld_32x32(o_addr, o0);
           tmem_ld_32x32(o_addr + 32, o1);
-          const uint32_t lp = tmem_ld_1(l_addr);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) fin_o[i] = o0[i], fin_o[32 + i] = o1[i];
-          fin_l = __uint_as_float(lp);
+          fin_l = l_run;
           fin_m = m_run;
           fin_valid = true;
         }
