@@ -163,76 +163,88 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
 
   if (warp == 0) {
     // ======================= TMA producer =======================
-    if (lane == 0) {
+    // all 32 lanes run the loop (addresses stay warp-uniform); the elected lane issues
+    const bool leader = elect_one();
+    if (leader) {
       tma_prefetch_desc(&p.q_map);
       mbar_arrive_expect_tx(q_full, 16384u * n_groups);
       for (int g = 0; g < n_groups; ++g)
         tma_load_3d(smem_base + AttnSmem::kQ + g * 16384, &p.q_map, q_full, head * kHeadDim, q_row0 + g * kTileQ, img);
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int j = 0; j < n_tiles; ++j) {
-        const int slot = (tile0 + j) / tiles_per_slot;
-        const int t0 = ((tile0 + j) % tiles_per_slot) * kTileKV;
-        if (!mbar_wait(kv_empty(stage), phase ^ 1u, abort_flag, p.dev_status, 400)) break;
+    }
+    __syncwarp();
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int slot = (tile0 + j) / tiles_per_slot;
+      const int t0 = ((tile0 + j) % tiles_per_slot) * kTileKV;
+      if (!mbar_wait_warp(kv_empty(stage), phase ^ 1u, abort_flag, p.dev_status, 400)) break;
+      if (leader) {
         mbar_arrive_expect_tx(kv_full(stage), 32768);
         tma_load_3d(smem_base + AttnSmem::kK + stage * 16384, &p.kv_map[slot], kv_full(stage), head * kHeadDim, t0, img);
         tma_load_3d(smem_base + AttnSmem::kV + stage * 16384, &p.kv_map[slot], kv_full(stage),
                     p.v_col0 + head * kHeadDim, t0, img);
-        if (++stage == kKvStages) {
-          stage = 0;
-          phase ^= 1u;
-        }
+      }
+      __syncwarp();
+      if (++stage == kKvStages) {
+        stage = 0;
+        phase ^= 1u;
       }
     }
   } else if (warp == 1) {
     // ======================= MMA issuer =======================
-    if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_f16(128, 128, 0, 0);  // S = Q K^T, both K-major
-      const uint32_t idesc_o = make_idesc_f16(128, 64, 0, 1);   // O = P V, V MN-major
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.dev_status, 500);
-      auto issue_s = [&](int j, int g) {
-        const int st = j % kKvStages;
-        const uint64_t qdesc = make_smem_desc_sw128(smem_base + AttnSmem::kQ + g * 16384, 16, 1024);
-        const uint64_t kdesc = make_smem_desc_sw128(smem_base + AttnSmem::kK + st * 16384, 16, 1024);
-        const uint32_t d = tmem_base + g * 128;
+    // all 32 lanes run the loop and the waits; the elected lane issues every tcgen05.mma and
+    // tcgen05.commit, so descriptors are formed from warp-uniform values
+    const bool leader = elect_one();
+    const uint32_t idesc_s = make_idesc_f16(128, 128, 0, 0);  // S = Q K^T, both K-major
+    const uint32_t idesc_o = make_idesc_f16(128, 64, 0, 1);   // O = P V, V MN-major
+    bool ok = mbar_wait_warp(q_full, 0, abort_flag, p.dev_status, 500);
+    auto issue_s = [&](int j, int g) {
+      const int st = j % kKvStages;
+      const uint64_t qdesc = make_smem_desc_sw128(smem_base + AttnSmem::kQ + g * 16384, 16, 1024);
+      const uint64_t kdesc = make_smem_desc_sw128(smem_base + AttnSmem::kK + st * 16384, 16, 1024);
+      const uint32_t d = tmem_base + g * 128;
+      if (leader) {
 #pragma unroll
         for (int k = 0; k < kHeadDim / 16; ++k) umma_f16(d, qdesc + 2u * k, kdesc + 2u * k, idesc_s, k != 0);
         umma_commit(s_full(g));
-      };
-      auto wait_kv = [&](int j) -> bool {
-        if (!mbar_wait(kv_full(j % kKvStages), (j / kKvStages) & 1u, abort_flag, p.dev_status, 501)) return false;
-        tc_fence_after_sync();
-        return true;
-      };
-      if (ok && n_tiles > 0) {
-        ok = wait_kv(0);
-        if (ok)
-          for (int g = 0; g < n_groups; ++g) issue_s(0, g);
       }
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int st = j % kKvStages;
-        // V tile [128 tokens][64] as stored: MN-major B operand, 8-token groups 1 KB apart
-        const uint64_t vdesc = make_smem_desc_sw128(smem_base + AttnSmem::kV + st * 16384, 16, 1024);
-        if (j + 1 < n_tiles && !wait_kv(j + 1)) break;
-        for (int g = 0; g < n_groups && ok; ++g) {
-          if (j + 1 < n_tiles) {
-            // the softmax group has copied S_g(j) into registers: the next Q K^T may overwrite it
-            if (!mbar_wait(s_free(g), j & 1u, abort_flag, p.dev_status, 503)) {
-              ok = false;
-              break;
-            }
-            tc_fence_after_sync();
-            issue_s(j + 1, g);
-          }
-          // P_g(j) is in tensor memory; O_g carries the right scale
-          if (!mbar_wait(p_full(g), j & 1u, abort_flag, p.dev_status, 502)) {
+      __syncwarp();
+    };
+    auto wait_kv = [&](int j) -> bool {
+      if (!mbar_wait_warp(kv_full(j % kKvStages), (j / kKvStages) & 1u, abort_flag, p.dev_status, 501)) return false;
+      tc_fence_after_sync();
+      return true;
+    };
+    if (ok && n_tiles > 0) {
+      ok = wait_kv(0);
+      if (ok)
+        for (int g = 0; g < n_groups; ++g) issue_s(0, g);
+    }
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int st = j % kKvStages;
+      // V tile [128 tokens][64] as stored: MN-major B operand, 8-token groups 1 KB apart
+      const uint64_t vdesc = make_smem_desc_sw128(smem_base + AttnSmem::kV + st * 16384, 16, 1024);
+      if (j + 1 < n_tiles && !wait_kv(j + 1)) break;
+      for (int g = 0; g < n_groups && ok; ++g) {
+        if (j + 1 < n_tiles) {
+          // the softmax group has copied S_g(j) into registers: the next Q K^T may overwrite it
+          if (!mbar_wait_warp(s_free(g), j & 1u, abort_flag, p.dev_status, 503)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t d = tmem_base + 256 + g * 64;
-          const uint32_t pt = tmem_base + 384 + g * 64;
-          const uint32_t acc = (j != 0);
+          issue_s(j + 1, g);
+        }
+        // P_g(j) is in tensor memory; O_g carries the right scale
+        if (!mbar_wait_warp(p_full(g), j & 1u, abort_flag, p.dev_status, 502)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d = tmem_base + 256 + g * 64;
+        const uint32_t pt = tmem_base + 384 + g * 64;
+        const uint32_t acc = (j != 0);
+        if (leader) {
 #pragma unroll
           for (int k = 0; k < kTileKV / 16; ++k) {
             // tokens 16k..16k+15: 8 packed columns of P, V rows advance by 16 x 128 B
@@ -241,6 +253,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
           umma_commit(o_full(g));
           if (g == n_groups - 1) umma_commit(kv_empty(st));  // K_j and V_j are no longer needed
         }
+        __syncwarp();
       }
     }
   } else {

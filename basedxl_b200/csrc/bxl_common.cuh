@@ -90,6 +90,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// One lane of a fully converged warp.  Producer and MMA warps run their loops with all 32
+// lanes (so that addresses and descriptors are warp-uniform values) and let the elected lane
+// issue the copy / MMA / commit instructions.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+// Bounded wait by every lane of a converged warp; true only if every lane saw the phase.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* dev_status,
+                                               int site) {
+  const bool ok = mbar_wait(bar, parity, abort_flag, dev_status, site);
+  return __all_sync(0xffffffffu, ok);
+}
+
 // ---- thread-block clusters / distributed shared memory ------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
