@@ -36,7 +36,9 @@
 
 namespace bxl {
 
-constexpr int kAttnThreads = 320;
+constexpr int kAttnThreads = 384;   // warps 0..7 softmax, 8 producer, 9 MMA issuer, 10..11 idle
+constexpr int kSoftmaxRegs = 216;   // registers per thread after the split: 8 x 32 x 216 + 4 x 32 x 72 = 64512
+constexpr int kOtherRegs = 72;
 constexpr int kHeadDim = 64;
 constexpr int kTileQ = 128;
 constexpr int kTileKV = 128;
@@ -58,8 +60,8 @@ struct alignas(64) AttnParams {
 };
 
 struct AttnSmem {
-  static constexpr int kQ = 0;                               // 2 x 16 KB
-  static constexpr int kK = 32768;                           // kKvStages x 16 KB
+  static constexpr int kQ = 0;                               // 2 buffers x 2 tiles x 16 KB
+  static constexpr int kK = 65536;                           // kKvStages x 16 KB
   static constexpr int kV = kK + kKvStages * 16384;          // kKvStages x 16 KB
   static constexpr int kBar = kV + kKvStages * 16384;
   static constexpr int kTotal = kBar + 1024 + 1024;
@@ -97,14 +99,15 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t bar_base = smem_base + AttnSmem::kBar;
-  // barriers: q_full, kv_full[3], kv_empty[3], s_full[2], o_full[2], p_full[2], s_free[2]
-  const uint32_t q_full = bar_base;
-  auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
-  auto kv_empty = [&](int s) { return bar_base + 8u * (1 + kKvStages + s); };
-  auto s_full = [&](int g) { return bar_base + 8u * (1 + 2 * kKvStages + g); };
-  auto o_full = [&](int g) { return bar_base + 8u * (3 + 2 * kKvStages + g); };
-  auto p_full = [&](int g) { return bar_base + 8u * (5 + 2 * kKvStages + g); };
-  auto s_free = [&](int g) { return bar_base + 8u * (7 + 2 * kKvStages + g); };
+  // barriers: q_full[2], q_empty[2], kv_full[stages], kv_empty[stages], s_full[2], o_full[2], p_full[2], s_free[2]
+  auto q_full = [&](int b) { return bar_base + 8u * b; };
+  auto q_empty = [&](int b) { return bar_base + 8u * (2 + b); };
+  auto kv_full = [&](int s) { return bar_base + 8u * (4 + s); };
+  auto kv_empty = [&](int s) { return bar_base + 8u * (4 + kKvStages + s); };
+  auto s_full = [&](int g) { return bar_base + 8u * (4 + 2 * kKvStages + g); };
+  auto o_full = [&](int g) { return bar_base + 8u * (6 + 2 * kKvStages + g); };
+  auto p_full = [&](int g) { return bar_base + 8u * (8 + 2 * kKvStages + g); };
+  auto s_free = [&](int g) { return bar_base + 8u * (10 + 2 * kKvStages + g); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + AttnSmem::kBar + 512);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + AttnSmem::kBar + 520);
 
@@ -115,29 +118,37 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
   // (P: 128 fp16 per row packed two per 32-bit column, the A operand of the P V product)
   constexpr uint32_t kTmemCols = 512;
 
-  // With kv_split = S > 1 the S CTAs of a cluster serve the same 256 queries, each over 1/S of
-  // the K/V tiles; their partial (max, sum, output) triples are merged through distributed
-  // shared memory at the end (every CTA merges 256/S of the rows).
+  // Work units: 256 queries (two tiles) of one (image, head).
+  //   kv_split == 1: the CTA walks units blockIdx.x, blockIdx.x + gridDim.x, ...; barriers, the
+  //     K/V ring and tensor memory live across units, Q is double buffered, so the loads and the
+  //     first Q K^T of the next unit overlap the tail of the current one.
+  //   kv_split == S > 1: the S CTAs of a cluster serve ONE unit, each over 1/S of the K/V tiles;
+  //     their partial (max, sum, output) triples are merged through distributed shared memory at
+  //     the end (every CTA merges 256/S of the rows).
   const int S = p.kv_split;
   const uint32_t crank = (S > 1) ? cluster_ctarank() : 0u;
-  const int work = blockIdx.x / S;
   const int q_pairs = (p.L_q + 2 * kTileQ - 1) / (2 * kTileQ);
-  const int qp = work % q_pairs;
-  const int head = (work / q_pairs) % p.heads;
-  const int img = work / (q_pairs * p.heads);
-  const int q_row0 = qp * 2 * kTileQ;
-  const int n_groups = (q_row0 + kTileQ < p.L_q) ? 2 : 1;   // the second tile may lie wholly past L_q
+  const int units_total = q_pairs * p.heads * p.B;
+  const int first_unit = (S > 1) ? static_cast<int>(blockIdx.x) / S : static_cast<int>(blockIdx.x);
+  const int unit_step = (S > 1) ? units_total : static_cast<int>(gridDim.x);
+  auto unit_q_row0 = [&](int w) { return (w % q_pairs) * 2 * kTileQ; };
+  auto unit_head = [&](int w) { return (w / q_pairs) % p.heads; };
+  auto unit_img = [&](int w) { return w / (q_pairs * p.heads); };
+  auto unit_groups = [&](int w) { return (unit_q_row0(w) + kTileQ < p.L_q) ? 2 : 1; };  // the second tile may lie wholly past L_q
   const int tiles_per_slot = (p.L_slot + kTileKV - 1) / kTileKV;
   const int total_tiles = p.n_slots * tiles_per_slot;
   const int tile0 = static_cast<int>((static_cast<long long>(crank) * total_tiles) / S);   // first K/V tile of this CTA
   const int n_tiles = static_cast<int>((static_cast<long long>(crank + 1) * total_tiles) / S) - tile0;
-  // per-thread result of the K/V loop (softmax threads), kept across the final hand-over
+  // kv_split > 1 only: per-thread result of the K/V loop (softmax threads), kept for the merge
   uint32_t fin_o[kHeadDim];
   float fin_l = 0.f, fin_m = -INFINITY;
   bool fin_valid = false;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(q_full(b), 1);
+      mbar_init(q_empty(b), 1);
+    }
     for (int s = 0; s < kKvStages; ++s) {
       mbar_init(kv_full(s), 1);
       mbar_init(kv_empty(s), 1);
@@ -151,7 +162,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 1) {
+  if (warp == 9) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
     tmem_relinquish();
   }
@@ -159,48 +170,82 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // the softmax warps hold a whole row of S (128 values) and of P: give them the registers the
+  // producer / MMA warpgroup does not need
   pdl_wait();  // the set-up above overlaps the previous kernel's tail; global data from here on
 
-  if (warp == 0) {
+  if (warp >= 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
+  if (warp == 8) {
     // ======================= TMA producer =======================
     // all 32 lanes run the loop (addresses stay warp-uniform); the elected lane issues
     const bool leader = elect_one();
-    if (leader) {
-      tma_prefetch_desc(&p.q_map);
-      mbar_arrive_expect_tx(q_full, 16384u * n_groups);
-      for (int g = 0; g < n_groups; ++g)
-        tma_load_3d(smem_base + AttnSmem::kQ + g * 16384, &p.q_map, q_full, head * kHeadDim, q_row0 + g * kTileQ, img);
-    }
+    if (leader) tma_prefetch_desc(&p.q_map);
     __syncwarp();
     int stage = 0;
     uint32_t phase = 0;
-    for (int j = 0; j < n_tiles; ++j) {
-      const int slot = (tile0 + j) / tiles_per_slot;
-      const int t0 = ((tile0 + j) % tiles_per_slot) * kTileKV;
-      if (!mbar_wait_warp(kv_empty(stage), phase ^ 1u, abort_flag, p.dev_status, 400)) break;
+    bool ok = true;
+    int ul = 0;  // units started by this CTA
+    for (int w = first_unit; w < units_total && ok; w += unit_step, ++ul) {
+      const int qb = ul & 1;
+      const int ng = unit_groups(w);
+      const int head = unit_head(w), img = unit_img(w), q_row0 = unit_q_row0(w);
+      // the Q buffer was last used by unit ul - 2: all its Q K^T products must have completed
+      if (ul >= 2 && !mbar_wait_warp(q_empty(qb), ((ul >> 1) - 1) & 1u, abort_flag, p.dev_status, 401)) break;
       if (leader) {
-        mbar_arrive_expect_tx(kv_full(stage), 32768);
-        tma_load_3d(smem_base + AttnSmem::kK + stage * 16384, &p.kv_map[slot], kv_full(stage), head * kHeadDim, t0, img);
-        tma_load_3d(smem_base + AttnSmem::kV + stage * 16384, &p.kv_map[slot], kv_full(stage),
-                    p.v_col0 + head * kHeadDim, t0, img);
+        mbar_arrive_expect_tx(q_full(qb), 16384u * ng);
+        for (int g = 0; g < ng; ++g)
+          tma_load_3d(smem_base + AttnSmem::kQ + qb * 32768 + g * 16384, &p.q_map, q_full(qb), head * kHeadDim,
+                      q_row0 + g * kTileQ, img);
       }
       __syncwarp();
-      if (++stage == kKvStages) {
-        stage = 0;
-        phase ^= 1u;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int slot = (tile0 + j) / tiles_per_slot;
+        const int t0 = ((tile0 + j) % tiles_per_slot) * kTileKV;
+        if (!mbar_wait_warp(kv_empty(stage), phase ^ 1u, abort_flag, p.dev_status, 400)) {
+          ok = false;
+          break;
+        }
+        if (leader) {
+          mbar_arrive_expect_tx(kv_full(stage), 32768);
+          tma_load_3d(smem_base + AttnSmem::kK + stage * 16384, &p.kv_map[slot], kv_full(stage), head * kHeadDim, t0, img);
+          tma_load_3d(smem_base + AttnSmem::kV + stage * 16384, &p.kv_map[slot], kv_full(stage),
+                      p.v_col0 + head * kHeadDim, t0, img);
+        }
+        __syncwarp();
+        if (++stage == kKvStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 9) {
     // ======================= MMA issuer =======================
     // all 32 lanes run the loop and the waits; the elected lane issues every tcgen05.mma and
-    // tcgen05.commit, so descriptors are formed from warp-uniform values
+    // tcgen05.commit, so descriptors are formed from warp-uniform values.  The K/V tiles of all
+    // units of this CTA form one stream: while the softmax of tile t runs, Q K^T of tile t+1 is
+    // issued, also across a unit boundary.
     const bool leader = elect_one();
     const uint32_t idesc_s = make_idesc_f16(128, 128, 0, 0);  // S = Q K^T, both K-major
     const uint32_t idesc_o = make_idesc_f16(128, 64, 0, 1);   // O = P V, V MN-major
-    bool ok = mbar_wait_warp(q_full, 0, abort_flag, p.dev_status, 500);
-    auto issue_s = [&](int j, int g) {
-      const int st = j % kKvStages;
-      const uint64_t qdesc = make_smem_desc_sw128(smem_base + AttnSmem::kQ + g * 16384, 16, 1024);
+    int n_s[2] = {0, 0};   // Q K^T products issued per group (= phases of s_full started)
+    int n_pv[2] = {0, 0};  // P V products issued per group
+    int kv_t = 0;          // K/V tiles of the stream consumed so far
+    bool ok = true;
+    auto wait_kv = [&](int t) -> bool {
+      if (!mbar_wait_warp(kv_full(t % kKvStages), (t / kKvStages) & 1u, abort_flag, p.dev_status, 501)) return false;
+      tc_fence_after_sync();
+      return true;
+    };
+    // S_g = Q_g K^T for stream tile t of the unit in Q buffer qb; S_g must have been read by the
+    // softmax group (s_free) if it was ever written
+    auto issue_s = [&](int qb, int g, int t) -> bool {
+      if (n_s[g] > 0) {
+        if (!mbar_wait_warp(s_free(g), (n_s[g] - 1) & 1u, abort_flag, p.dev_status, 503)) return false;
+        tc_fence_after_sync();
+      }
+      const int st = t % kKvStages;
+      const uint64_t qdesc = make_smem_desc_sw128(smem_base + AttnSmem::kQ + qb * 32768 + g * 16384, 16, 1024);
       const uint64_t kdesc = make_smem_desc_sw128(smem_base + AttnSmem::kK + st * 16384, 16, 1024);
       const uint32_t d = tmem_base + g * 128;
       if (leader) {
@@ -209,72 +254,105 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
         umma_commit(s_full(g));
       }
       __syncwarp();
-    };
-    auto wait_kv = [&](int j) -> bool {
-      if (!mbar_wait_warp(kv_full(j % kKvStages), (j / kKvStages) & 1u, abort_flag, p.dev_status, 501)) return false;
-      tc_fence_after_sync();
+      ++n_s[g];
       return true;
     };
-    if (ok && n_tiles > 0) {
-      ok = wait_kv(0);
-      if (ok)
-        for (int g = 0; g < n_groups; ++g) issue_s(0, g);
+    int ul = 0;
+    if (first_unit < units_total) {
+      // first tile of the first unit
+      ok = mbar_wait_warp(q_full(0), 0, abort_flag, p.dev_status, 500) && wait_kv(0);
+      for (int g = 0; g < unit_groups(first_unit) && ok; ++g) ok = issue_s(0, g, 0);
     }
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int st = j % kKvStages;
-      // V tile [128 tokens][64] as stored: MN-major B operand, 8-token groups 1 KB apart
-      const uint64_t vdesc = make_smem_desc_sw128(smem_base + AttnSmem::kV + st * 16384, 16, 1024);
-      if (j + 1 < n_tiles && !wait_kv(j + 1)) break;
-      for (int g = 0; g < n_groups && ok; ++g) {
+    for (int w = first_unit; w < units_total && ok; w += unit_step, ++ul) {
+      const int qb = ul & 1;
+      const int ng = unit_groups(w);
+      const int w_next = w + unit_step;
+      const bool has_next_unit = w_next < units_total;
+      for (int j = 0; j < n_tiles && ok; ++j, ++kv_t) {
+        const int st = kv_t % kKvStages;
+        // V tile [128 tokens][64] as stored: MN-major B operand, 8-token groups 1 KB apart
+        const uint64_t vdesc = make_smem_desc_sw128(smem_base + AttnSmem::kV + st * 16384, 16, 1024);
+        // the tile after this one in the stream
+        int nxt_ng = 0, nxt_qb = qb;
         if (j + 1 < n_tiles) {
-          // the softmax group has copied S_g(j) into registers: the next Q K^T may overwrite it
-          if (!mbar_wait_warp(s_free(g), j & 1u, abort_flag, p.dev_status, 503)) {
-            ok = false;
-            break;
+          nxt_ng = ng;
+        } else {
+          // every Q K^T of this unit has been issued: its Q buffer is free once they complete
+          if (leader) umma_commit(q_empty(qb));
+          __syncwarp();
+          if (has_next_unit) {
+            nxt_ng = unit_groups(w_next), nxt_qb = qb ^ 1;
+            if (!mbar_wait_warp(q_full(nxt_qb), ((ul + 1) >> 1) & 1u, abort_flag, p.dev_status, 500)) {
+              ok = false;
+              break;
+            }
           }
-          tc_fence_after_sync();
-          issue_s(j + 1, g);
         }
-        // P_g(j) is in tensor memory; O_g carries the right scale
-        if (!mbar_wait_warp(p_full(g), j & 1u, abort_flag, p.dev_status, 502)) {
+        if (nxt_ng > 0 && !wait_kv(kv_t + 1)) {
           ok = false;
           break;
         }
-        tc_fence_after_sync();
-        const uint32_t d = tmem_base + 256 + g * 64;
-        const uint32_t pt = tmem_base + 384 + g * 64;
-        const uint32_t acc = (j != 0);
-        if (leader) {
+        for (int g = 0; g < 2 && ok; ++g) {
+          if (g < nxt_ng) ok = issue_s(nxt_qb, g, kv_t + 1);
+          if (g < ng && ok) {
+            // P_g of this tile is in tensor memory; O_g carries the right scale
+            if (!mbar_wait_warp(p_full(g), n_pv[g] & 1u, abort_flag, p.dev_status, 502)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            const uint32_t d = tmem_base + 256 + g * 64;
+            const uint32_t pt = tmem_base + 384 + g * 64;
+            const uint32_t acc = (j != 0);
+            if (leader) {
 #pragma unroll
-          for (int k = 0; k < kTileKV / 16; ++k) {
-            // tokens 16k..16k+15: 8 packed columns of P, V rows advance by 16 x 128 B
-            umma_f16_ts(d, pt + 8u * k, vdesc + 128u * k, idesc_o, acc | k);
+              for (int k = 0; k < kTileKV / 16; ++k) {
+                // tokens 16k..16k+15: 8 packed columns of P, V rows advance by 16 x 128 B
+                umma_f16_ts(d, pt + 8u * k, vdesc + 128u * k, idesc_o, acc | k);
+              }
+              umma_commit(o_full(g));
+            }
+            __syncwarp();
+            ++n_pv[g];
           }
-          umma_commit(o_full(g));
-          if (g == n_groups - 1) umma_commit(kv_empty(st));  // K_j and V_j are no longer needed
         }
-        __syncwarp();
+        // K and V of this tile are no longer needed once everything issued so far has completed
+        if (ok) {
+          if (leader) umma_commit(kv_empty(st));
+          __syncwarp();
+        }
       }
     }
+  }
+    // producer / MMA warpgroup: the barriers of the hand-over, nothing to merge
+    tc_fence_before_sync();
+    __syncthreads();
+    if (S > 1) {
+      cluster_sync_all();
+      cluster_sync_all();
+    }
   } else {
-    // ======================= softmax / output (warps 2..9) =======================
-    const int g = (warp - 2) >> 2;         // query tile served by this warp
+    // ======================= softmax / output (warps 0..7) =======================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
+    const int g = warp >> 2;               // query tile served by this warp
     const int quarter = warp & 3;          // TMEM lane quarter this warp may access
     const int row = quarter * 32 + lane;   // query row inside the tile == TMEM lane
-    if (g < n_groups) {
-      const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-      const uint32_t s_addr = t_lane + g * 128;
-      const uint32_t o_addr = t_lane + 256 + g * 64;
-      const uint32_t p_addr = t_lane + 384 + g * 64;
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t s_addr = t_lane + g * 128;
+    const uint32_t o_addr = t_lane + 256 + g * 64;
+    const uint32_t p_addr = t_lane + 384 + g * 64;
+    const float sc = p.scale_log2e;
+    constexpr float kRaise = 8.f;  // raise m only when the tile maximum exceeds it by 2^8
+    int cnt = 0;                   // K/V tiles this group has processed (all units)
+    bool ok = true;
+    for (int w = first_unit; w < units_total && ok; w += unit_step) {
+      if (g >= unit_groups(w)) continue;
       float m_run = -INFINITY;   // running row maximum in the exp2 domain (score * scale * log2 e)
       float l_run = 0.f;         // running row sum of P, same reference as O
-      const float sc = p.scale_log2e;
-      constexpr float kRaise = 8.f;  // raise m only when the tile maximum exceeds it by 2^8
-      bool ok = true;
-      for (int j = 0; j < n_tiles && ok; ++j) {
+      for (int j = 0; j < n_tiles && ok; ++j, ++cnt) {
         const int t0 = ((tile0 + j) % tiles_per_slot) * kTileKV;
         const int valid = min(kTileKV, p.L_slot - t0);
-        if (!mbar_wait(s_full(g), j & 1u, abort_flag, p.dev_status, 600)) {
+        if (!mbar_wait(s_full(g), cnt & 1u, abort_flag, p.dev_status, 600)) {
           ok = false;
           break;
         }
@@ -349,9 +427,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
         }
         l_run = fmaf(l_run, alpha, (sum0 + sum1) + (sum2 + sum3));
         // the previous tile's P V product must have finished: it read the P buffer, and O is only
-        // touched between two products
+        // touched between two products (for the first tile of a unit this was awaited when the
+        // previous unit's output was read)
         if (j > 0) {
-          if (!mbar_wait(o_full(g), (j - 1) & 1u, abort_flag, p.dev_status, 601)) {
+          if (!mbar_wait(o_full(g), (cnt - 1) & 1u, abort_flag, p.dev_status, 601)) {
             ok = false;
             break;
           }
@@ -371,94 +450,113 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
             tmem_st_32x32(o_addr + 32, o1);
           }
         }
-        // publish P(j) in tensor memory
+        // publish P in tensor memory
         tmem_st_32x32(p_addr, pa);
         tmem_st_32x32(p_addr + 32, pb);
         tmem_st_wait();
         tc_fence_before_sync();
         mbar_arrive(p_full(g));
       }
-      if (ok && n_tiles > 0) {
-        const int j = n_tiles - 1;
-        if (mbar_wait(o_full(g), j & 1u, abort_flag, p.dev_status, 602)) {
-          __syncwarp();
-          tc_fence_after_sync();
-          uint32_t o0[32], o1[32];
-          tmem_ld_32x32(o_addr, o0);
-          tmem_ld_32x32(o_addr + 32, o1);
-          tmem_ld_wait();
+      if (!ok) break;
+      // ---- end of the unit: O_g is complete once the last P V product has finished ----
+      if (!mbar_wait(o_full(g), (cnt - 1) & 1u, abort_flag, p.dev_status, 602)) {
+        ok = false;
+        break;
+      }
+      __syncwarp();
+      tc_fence_after_sync();
+      uint32_t o0[32], o1[32];
+      tmem_ld_32x32(o_addr, o0);
+      tmem_ld_32x32(o_addr + 32, o1);
+      tmem_ld_wait();
+      if (S > 1) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) fin_o[i] = o0[i], fin_o[32 + i] = o1[i];
-          fin_l = l_run;
-          fin_m = m_run;
-          fin_valid = true;
+        for (int i = 0; i < 32; ++i) fin_o[i] = o0[i], fin_o[32 + i] = o1[i];
+        fin_l = l_run;
+        fin_m = m_run;
+        fin_valid = true;
+      } else {
+        const int q_row = unit_q_row0(w) + g * kTileQ + row;
+        if (q_row < p.L_q) {
+          const float inv_l = 1.f / l_run;
+          __half* dst = p.out + (long long)unit_img(w) * p.out_img_stride + (long long)q_row * p.ld_out + unit_head(w) * kHeadDim;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 u0, u1;
+            u0.x = pack_f16x2(__uint_as_float(o0[8 * q]) * inv_l, __uint_as_float(o0[8 * q + 1]) * inv_l);
+            u0.y = pack_f16x2(__uint_as_float(o0[8 * q + 2]) * inv_l, __uint_as_float(o0[8 * q + 3]) * inv_l);
+            u0.z = pack_f16x2(__uint_as_float(o0[8 * q + 4]) * inv_l, __uint_as_float(o0[8 * q + 5]) * inv_l);
+            u0.w = pack_f16x2(__uint_as_float(o0[8 * q + 6]) * inv_l, __uint_as_float(o0[8 * q + 7]) * inv_l);
+            u1.x = pack_f16x2(__uint_as_float(o1[8 * q]) * inv_l, __uint_as_float(o1[8 * q + 1]) * inv_l);
+            u1.y = pack_f16x2(__uint_as_float(o1[8 * q + 2]) * inv_l, __uint_as_float(o1[8 * q + 3]) * inv_l);
+            u1.z = pack_f16x2(__uint_as_float(o1[8 * q + 4]) * inv_l, __uint_as_float(o1[8 * q + 5]) * inv_l);
+            u1.w = pack_f16x2(__uint_as_float(o1[8 * q + 6]) * inv_l, __uint_as_float(o1[8 * q + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(dst + q * 8) = u0;
+            *reinterpret_cast<uint4*>(dst + 32 + q * 8) = u1;
+          }
+        }
+      }
+    }
+    // ---- kv_split > 1: merge the partial results of the cluster and write the output -------
+    // (the producer / MMA warps take part in the same three barriers in their own branch)
+    tc_fence_before_sync();
+    __syncthreads();
+    if (S > 1) {
+      const int w = first_unit;
+      const int n_groups = unit_groups(w);
+      const bool softmax_thread = (warp < 8) && ((warp >> 2) < n_groups);
+      const int sg = warp >> 2, srow = (warp & 3) * 32 + lane;     // group and row of a softmax thread
+      const int grow = sg * kTileQ + srow;                                 // row within the unit's 256 queries
+      // every CTA of the cluster has left its K/V loop: the K/V ring of each CTA is free and serves
+      // as the receive buffer  [sender][66 values][rows owned] (fp32)
+      cluster_sync_all();
+      const int rows_owned = 2 * kTileQ / S;
+      const uint32_t owner = softmax_thread ? static_cast<uint32_t>(grow / rows_owned) : 0u;
+      const int lrow = grow % rows_owned;
+      const uint32_t recv = smem_base + AttnSmem::kK;
+      if (softmax_thread && owner != crank && fin_valid) {
+        const uint32_t slot = (crank < owner) ? crank : crank - 1;
+        const uint32_t base = map_to_cta(recv + ((slot * 66u) * rows_owned + lrow) * 4u, owner);
+        const uint32_t stride = rows_owned * 4u;
+  #pragma unroll
+        for (int i = 0; i < kHeadDim; ++i) st_cluster_f32(base + i * stride, __uint_as_float(fin_o[i]));
+        st_cluster_f32(base + 64u * stride, fin_l);
+        st_cluster_f32(base + 65u * stride, fin_m);
+      }
+      cluster_sync_all();  // all partials have landed
+      if (softmax_thread && owner == crank && fin_valid) {
+        const float* rbuf = reinterpret_cast<const float*>(smem_gen + AttnSmem::kK);
+        float m_all = fin_m;
+        for (int s2 = 0; s2 < S - 1; ++s2) m_all = fmaxf(m_all, rbuf[(s2 * 66 + 65) * rows_owned + lrow]);
+        const float own_scale = fast_exp2(fin_m - m_all);
+        float l_all = fin_l * own_scale;
+        float acc[kHeadDim];
+  #pragma unroll
+        for (int i = 0; i < kHeadDim; ++i) acc[i] = __uint_as_float(fin_o[i]) * own_scale;
+        for (int s2 = 0; s2 < S - 1; ++s2) {
+          const float* rb = rbuf + (s2 * 66) * rows_owned + lrow;
+          const float sc2 = fast_exp2(rb[65 * rows_owned] - m_all);
+          l_all = fmaf(rb[64 * rows_owned], sc2, l_all);
+  #pragma unroll
+          for (int i = 0; i < kHeadDim; ++i) acc[i] = fmaf(rb[i * rows_owned], sc2, acc[i]);
+        }
+        const int q_row = unit_q_row0(w) + grow;
+        if (q_row < p.L_q) {
+          const float inv_l = 1.f / l_all;
+          __half* dst = p.out + (long long)unit_img(w) * p.out_img_stride + (long long)q_row * p.ld_out + unit_head(w) * kHeadDim;
+  #pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            uint4 u;
+            u.x = pack_f16x2(acc[q * 8] * inv_l, acc[q * 8 + 1] * inv_l);
+            u.y = pack_f16x2(acc[q * 8 + 2] * inv_l, acc[q * 8 + 3] * inv_l);
+            u.z = pack_f16x2(acc[q * 8 + 4] * inv_l, acc[q * 8 + 5] * inv_l);
+            u.w = pack_f16x2(acc[q * 8 + 6] * inv_l, acc[q * 8 + 7] * inv_l);
+            *reinterpret_cast<uint4*>(dst + q * 8) = u;
+          }
         }
       }
     }
   }
-
-  // ---- hand-over: merge the K/V splits (if any) and write the output ----------------
-  tc_fence_before_sync();
-  __syncthreads();
-  const bool softmax_thread = (warp >= 2) && (((warp - 2) >> 2) < n_groups);
-  const int sg = (warp - 2) >> 2, srow = (warp & 3) * 32 + lane;     // group and row of a softmax thread
-  const int grow = sg * kTileQ + srow;                                 // row within the CTA's 256 queries
-  if (S > 1) {
-    // every CTA of the cluster has left its K/V loop: the K/V ring of each CTA is free and serves
-    // as the receive buffer  [sender][66 values][rows owned] (fp32)
-    cluster_sync_all();
-    const int rows_owned = 2 * kTileQ / S;
-    const uint32_t owner = softmax_thread ? static_cast<uint32_t>(grow / rows_owned) : 0u;
-    const int lrow = grow % rows_owned;
-    const uint32_t recv = smem_base + AttnSmem::kK;
-    if (softmax_thread && owner != crank && fin_valid) {
-      const uint32_t slot = (crank < owner) ? crank : crank - 1;
-      const uint32_t base = map_to_cta(recv + ((slot * 66u) * rows_owned + lrow) * 4u, owner);
-      const uint32_t stride = rows_owned * 4u;
-#pragma unroll
-      for (int i = 0; i < kHeadDim; ++i) st_cluster_f32(base + i * stride, __uint_as_float(fin_o[i]));
-      st_cluster_f32(base + 64u * stride, fin_l);
-      st_cluster_f32(base + 65u * stride, fin_m);
-    }
-    cluster_sync_all();  // all partials have landed
-    if (softmax_thread && owner == crank && fin_valid) {
-      const float* rbuf = reinterpret_cast<const float*>(smem_gen + AttnSmem::kK);
-      float m_all = fin_m;
-      for (int s2 = 0; s2 < S - 1; ++s2) m_all = fmaxf(m_all, rbuf[(s2 * 66 + 65) * rows_owned + lrow]);
-      const float own_scale = fast_exp2(fin_m - m_all);
-      float l_all = fin_l * own_scale;
-      float acc[kHeadDim];
-#pragma unroll
-      for (int i = 0; i < kHeadDim; ++i) acc[i] = __uint_as_float(fin_o[i]) * own_scale;
-      for (int s2 = 0; s2 < S - 1; ++s2) {
-        const float* rb = rbuf + (s2 * 66) * rows_owned + lrow;
-        const float sc2 = fast_exp2(rb[65 * rows_owned] - m_all);
-        l_all = fmaf(rb[64 * rows_owned], sc2, l_all);
-#pragma unroll
-        for (int i = 0; i < kHeadDim; ++i) acc[i] = fmaf(rb[i * rows_owned], sc2, acc[i]);
-      }
-      fin_l = l_all;
-#pragma unroll
-      for (int i = 0; i < kHeadDim; ++i) fin_o[i] = __float_as_uint(acc[i]);
-    }
-  }
-  if (softmax_thread && fin_valid && (S == 1 || static_cast<uint32_t>(grow / (2 * kTileQ / S)) == crank)) {
-    const int q_row = q_row0 + grow;
-    if (q_row < p.L_q) {
-      const float inv_l = 1.f / fin_l;
-      __half* dst = p.out + (long long)img * p.out_img_stride + (long long)q_row * p.ld_out + head * kHeadDim;
-#pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        uint4 u;
-        __half2* h = reinterpret_cast<__half2*>(&u);
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          h[i] = __floats2half2_rn(__uint_as_float(fin_o[q * 8 + 2 * i]) * inv_l, __uint_as_float(fin_o[q * 8 + 2 * i + 1]) * inv_l);
-        *reinterpret_cast<uint4*>(dst + q * 8) = u;
-      }
-    }
-  }
-
   // ---- teardown ---------------------------------------------------------------
   tc_fence_before_sync();
   __syncthreads();
@@ -467,7 +565,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
     while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 1) {
+  if (warp == 9) {
     __syncwarp();
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -534,18 +632,20 @@ extern "C" int bxl_attn_fwd_f16(const void* q, long long q_img_stride, long long
   const int q_pairs = (L_q + 2 * kTileQ - 1) / (2 * kTileQ);
   const int work = q_pairs * heads * B;
   const int total_tiles = n_slots * ((L_slot + kTileKV - 1) / kTileKV);
-  // K/V split: fewest rounds x tiles per round, with a fixed per-CTA cost of ~2.5 tiles and
-  // ~1.5 tiles for the merge
+  // K/V split: fewest rounds x tiles per round.  Without a split a CTA walks several units and
+  // pays ~1 tile of bubble per unit plus ~2.5 once; with a split each cluster serves one unit and
+  // pays ~2.5 tiles of set-up and ~1.5 for the merge.
   int split = 1;
   double best = 1e30;
   for (int s2 = 1; s2 <= 4; s2 *= 2) {
     if (s2 > total_tiles || (g_force_attn_split && s2 != g_force_attn_split)) continue;
     const int clusters = sm_count() / s2;
     const int rounds = (work + clusters - 1) / clusters;
-    const double cost = rounds * ((total_tiles + s2 - 1) / s2 + 2.5 + (s2 > 1 ? 1.5 : 0.0));
+    const double cost = (s2 == 1) ? rounds * (total_tiles + 1.0) + 2.5 : rounds * ((total_tiles + s2 - 1) / s2 + 2.5 + 1.5);
     if (cost < best - 1e-9) best = cost, split = s2;
   }
   p.kv_split = split;
-  return launch_kernel("attention_kernel launch", attention_kernel, dim3(work * split), dim3(kAttnThreads), AttnSmem::kTotal,
+  const int grid = (split == 1) ? (work < sm_count() ? work : sm_count()) : work * split;
+  return launch_kernel("attention_kernel launch", attention_kernel, dim3(grid), dim3(kAttnThreads), AttnSmem::kTotal,
                        (cudaStream_t)stream, split, p);
 }
