@@ -183,8 +183,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + 2 + a); };
   const uint32_t recv_full_bar = bar_base + 8u * (2 * kMaxStages + 4);
   const uint32_t recv_free_bar = bar_base + 8u * (2 * kMaxStages + 5);
-  // pair mode: the odd CTA reports "my half of stage s has landed" on the leader's pfull[s]
-  auto pfull_bar = [&](int s) { return bar_base + 8u * (2 * kMaxStages + 6 + s); };
   uint8_t* misc = smem_gen + (bar_base - smem_base) + 256;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 8);
@@ -200,7 +198,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
       // one arrival (with its byte count) from each of this CTA's two producer threads
       mbar_init(full_bar(s), 2);
       mbar_init(empty_bar(s), 1);
-      mbar_init(pfull_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
@@ -238,8 +235,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
   const int kb_per_seg = kConv ? 9 * (p.cCin / kBK) : (p.K + kBK - 1) / kBK;
   const int num_kb = kConv ? kb_per_seg : kb_per_seg * p.nseg;
   // this CTA's share of the K loop (balanced; never empty because split <= num_kb)
-  const int kb_begin = static_cast<int>((static_cast<long long>(crank) * num_kb) / S);
-  const int kb_end = static_cast<int>((static_cast<long long>(crank + 1) * num_kb) / S);
+  const uint32_t krank = kPair ? 0u : crank;  // both CTAs of a pair walk the whole K range
+  const int kb_begin = static_cast<int>((static_cast<long long>(krank) * num_kb) / S);
+  const int kb_end = static_cast<int>((static_cast<long long>(krank + 1) * num_kb) / S);
   const int first_tile = blockIdx.x / (S * kWidth);
   const int tile_step = gridDim.x / (S * kWidth);
 
@@ -276,9 +274,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
           }
           const uint32_t a_dst = smem_base + stage * stage_bytes;
           const uint32_t b_dst = a_dst + kABytes;
-          const uint32_t fbar = full_bar(stage);
+          // pair mode: both CTAs report their bytes to the leader's barrier; the leader's two
+          // producer threads announce the bytes of both halves
+          const uint32_t fbar = kPair ? map_to_cta(full_bar(stage), 0) : full_bar(stage);
+          const bool announces = !kPair || crank == 0;
+          auto load_2d = [&](uint32_t dst, const CUtensorMap* m, int c0, int c1) {
+            if (kPair) tma_load_2d_pair(dst, m, fbar, c0, c1);
+            else tma_load_2d(dst, m, fbar, c0, c1);
+          };
+          auto load_5d = [&](uint32_t dst, const CUtensorMap* m, int c0, int c1, int c2, int c3, int c4) {
+            if (kPair) tma_load_5d_pair(dst, m, fbar, c0, c1, c2, c3, c4);
+            else tma_load_5d(dst, m, fbar, c0, c1, c2, c3, c4);
+          };
           if (loads_a) {
-            mbar_arrive_expect_tx(fbar, kABytes);
+            if (announces) mbar_arrive_expect_tx(full_bar(stage), kABytes * kWidth);
             if (kConv) {
               const int cchunks = p.cCin / kBK;
               const int tap = kb / cchunks;
@@ -297,33 +306,33 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
               if (p.cStride == 1 && !touches_halo) {
                 // all th input rows come from the body (rows outside [0, H) are zero-filled by
                 // the copy engine): one copy for the whole A tile
-                tma_load_5d(a_dst, &p.a_rows_map, fbar, c0, par, x0 + xoff, r_first, img);
+                load_5d(a_dst, &p.a_rows_map, c0, par, x0 + xoff, r_first, img);
               } else {
                 for (int t = 0; t < p.th; ++t) {
                   const int r_in = p.cStride * (y0 + t) + ky - 1;
                   const uint32_t dst = a_dst + t * p.tw * 128;
                   const CUtensorMap* src = (r_in == -1 && p.has_top) ? &p.a_map[1] : (r_in == p.cHin && p.has_bot) ? &p.a_map[2] : &p.a_map[0];
                   const int r_src = (src == &p.a_map[0]) ? r_in : 0;
-                  tma_load_5d(dst, src, fbar, c0, par, x0 + xoff, r_src, img);
+                  load_5d(dst, src, c0, par, x0 + xoff, r_src, img);
                 }
               }
             } else {
               const int seg = kb / kb_per_seg;
               const int k0 = (kb % kb_per_seg) * kBK;
-              tma_load_2d(a_dst, &p.a_map[seg], fbar, k0, tm * kBM);
+              load_2d(a_dst, &p.a_map[seg], k0, tm * kBM);
             }
           } else {
-            mbar_arrive_expect_tx(fbar, b_rows * 128);
+            if (announces) mbar_arrive_expect_tx(full_bar(stage), b_rows * 128 * kWidth);
             if (kConv) {
-              tma_load_2d(b_dst, &p.b_map[0], fbar, kb * kBK, n0);
+              load_2d(b_dst, &p.b_map[0], kb * kBK, n0);
             } else {
               const int seg = kb / kb_per_seg;
               const int k0 = (kb % kb_per_seg) * kBK;
               if (p.b_kn) {
                 // B[K,N]: one 64(n) x 64(k) box per 64 output columns
-                for (int j = 0; j < b_rows / 64; ++j) tma_load_2d(b_dst + j * 8192, &p.b_map[seg], fbar, n0 + j * 64, k0);
+                for (int j = 0; j < b_rows / 64; ++j) load_2d(b_dst + j * 8192, &p.b_map[seg], n0 + j * 64, k0);
               } else {
-                tma_load_2d(b_dst, &p.b_map[seg], fbar, k0, n0);
+                load_2d(b_dst, &p.b_map[seg], k0, n0);
               }
             }
           }
@@ -337,25 +346,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
   } else if (warp == 1) {
     // ======================= MMA issuer =======================
     if (kPair && crank != 0) {
-      // odd CTA of a pair: report every landed stage to the leader, which issues the MMAs for both
-      if (lane == 0) {
-        int stage = 0;
-        uint32_t phase = 0;
-        bool ok = true;
-        for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
-          for (int kb = kb_begin; kb < kb_end; ++kb) {
-            if (!mbar_wait(full_bar(stage), phase, abort_flag, p.dev_status, 210)) {
-              ok = false;
-              break;
-            }
-            mbar_arrive_remote(map_to_cta(pfull_bar(stage), 0));
-            if (++stage == p.stages) {
-              stage = 0;
-              phase ^= 1u;
-            }
-          }
-        }
-      }
+      // odd CTA of a pair: the leader issues the MMAs for both
     } else if (lane == 0) {
       const uint32_t idesc = make_idesc_f16(kBM * kWidth, BN, 0, (!kConv && p.b_kn) ? 1 : 0);
       int stage = 0;
@@ -371,8 +362,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.dev_status, 201) ||
-              (kPair && !mbar_wait_cluster(pfull_bar(stage), phase, abort_flag, p.dev_status, 202))) {
+          if (kPair ? !mbar_wait_cluster(full_bar(stage), phase, abort_flag, p.dev_status, 201)
+                    : !mbar_wait(full_bar(stage), phase, abort_flag, p.dev_status, 201)) {
             ok = false;
             break;
           }
@@ -556,14 +547,17 @@ static int stages_for(int bn, int split, int pair = 0) {
   return st;
 }
 
-// Pick the tile width, the K split and whether to pair CTAs, minimising a time model
-// calibrated on B200.  One CTA streams its operands at ~98 KB/us from L2 (the per-SM fill
-// rate is what bounds these kernels, not the tensor pipe), so a k-block of a 128 x bn tile
-// costs max(mma(bn), bytes / 98 KB/us) with bytes = 16 KB + bn*128 B, or 16 KB + bn*64 B when
-// two CTAs share the B tile.  A wider tile or a CTA pair moves fewer bytes per FLOP; a
-// narrower tile or a K split spreads the stream over more SMs when there are few tiles.
+// Pick the tile width, the K split and whether to pair CTAs, minimising a time model fitted
+// to a sweep of every (tile width, split, pairing) over the GEMM and convolution shapes of the
+// SDXL UNet on B200.  One CTA streams its operands at ~110 KB/us from L2 (the per-SM fill rate
+// bounds these kernels, not the tensor pipe), so a k-block of a 128 x bn tile costs
+// max(mma(bn), bytes / 110 KB/us) with bytes = 16 KB + bn*128 B.  A CTA pair moves half of the B
+// tile per CTA but its stage recycling crosses two SMs: 0.24 us + 0.63 ns * bn per k-block.
+// `a_min_us` is a floor per k-block for the A operand path (the multi-row image copies of the
+// convolution).  A wider tile or a pair moves fewer bytes per FLOP; a narrower tile or a K split
+// spreads the stream over more SMs when there are few tiles.
 static TileConfig choose_tiles(int tiles_m, int N, int num_kb, bool b_kn, int force_bn = 0, int force_split = 0,
-                               int force_pair = -1) {
+                               int force_pair = -1, double a_min_us = 0.0) {
   const int sms = sm_count();
   TileConfig best{128, 1, stages_for(128, 1), 0};
   double best_cost = 1e30;
@@ -584,9 +578,9 @@ static TileConfig choose_tiles(int tiles_m, int N, int num_kb, bool b_kn, int fo
         const int par = tiles < clusters ? tiles : clusters;
         const int rounds = (tiles + par - 1) / par;
         const double bytes = 16384.0 + bn * (pair ? 64.0 : 128.0);
-        const double kb_us = fmax(bn / 256.0 * 0.27, bytes / 98000.0);
+        const double kb_us = fmax(fmax(bn / 256.0 * 0.27, pair ? 0.24 + 0.00063 * bn : bytes / 110000.0), a_min_us);
         const double kb_unit = (num_kb + split - 1) / split;
-        const double epi_us = 0.12 * (bn / 32.0) / split + (split > 1 ? 1.2 : 0.0);  // accumulator read-out (+ exchange)
+        const double epi_us = 0.08 * (bn / 32.0) / split + (split > 1 ? 1.2 : 0.0);  // accumulator read-out (+ exchange)
         const double fill_us = 1.0 + (st < 4 ? 0.5 : 0.0) + (pair ? 0.3 : 0.0);       // pipeline ramp per unit
         const double cost = rounds * (kb_unit * kb_us + epi_us) + fill_us + 3.0;
         if (cost < best_cost - 1e-9) {
@@ -630,8 +624,8 @@ static int launch(const GemmParams& p, int tiles_m, int tiles_n, cudaStream_t st
 static int aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // test hook: force the tile width / K split (0 = choose)
-// CTA pairing stays off unless asked for until the model below is trusted to choose it
-constexpr int kDefaultPair = 0;  // -1 = let the cost model decide
+constexpr int kDefaultPair = -1;  // -1 = let the cost model decide
+constexpr double kConvAMinUs = 0.36;  // per-k-block floor of the convolution's image copies
 static int g_force_bn = 0, g_force_split = 0, g_force_pair = -1;
 
 }  // namespace bxl
@@ -901,7 +895,8 @@ extern "C" int bxl_conv3x3_halo_f16(const void* x, long long x_img_stride, const
   if (int rc = enc(&p.a_map[2], bot ? bot : x, 1, bot ? halo_img_stride : x_img_stride)) return rc;
   const int K = 9 * C_in;
   const int tiles_x = (W_out + tw - 1) / tw, tiles_y = (H_out + th - 1) / th;
-  const TileConfig tc = choose_tiles(B * tiles_x * tiles_y, C_out, K / kBK, false, g_force_bn, g_force_split, g_force_pair < 0 ? kDefaultPair : g_force_pair);
+  const TileConfig tc = choose_tiles(B * tiles_x * tiles_y, C_out, K / kBK, false, g_force_bn, g_force_split,
+                                     g_force_pair < 0 ? kDefaultPair : g_force_pair, kConvAMinUs);
   const int BN = tc.bn;
   {
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)C_out};

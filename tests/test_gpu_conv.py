@@ -168,8 +168,11 @@ def test_halo_pack_is_bit_exact():
     _lib.device_status()
 
 
-@pytest.mark.parametrize("bn,split", [(64, 1), (160, 1), (256, 1), (128, 2), (128, 4), (256, 4)])
-def test_conv_forced_tile_width_and_k_split(bn, split):
+@pytest.mark.parametrize("bn,split,pair", [(64, 1, 0), (160, 1, 0), (256, 1, 0), (128, 2, 0), (128, 4, 0), (256, 4, 0),
+                                           (128, 1, 1), (160, 1, 1), (256, 1, 1)])
+def test_conv_forced_tile_width_and_k_split(bn, split, pair):
+    """Every tile width, K split and the CTA-pair form (two CTAs, one MMA stream) on a conv with
+    stale halo rows; the pair's second tile partly lies past the last image."""
     dev = cuda_or_skip()
     _lib, ops = _ops()
     gen = torch.Generator().manual_seed(bn + split)
@@ -180,14 +183,14 @@ def test_conv_forced_tile_width_and_k_split(bn, split):
     xs, xps = torch.chunk(x, 2, 2), torch.chunk(xp, 2, 2)
     stale = [po.conv2d_boundary(t, 1) for t in xps]
     l = _lib.lib()
-    _lib.check(l.bxl_debug_force_tiles(bn, split, -1), l, kernels=0)
+    _lib.check(l.bxl_debug_force_tiles(bn, split, pair), l, kernels=0)
     try:
         for i in range(2):
             ref = po.conv2d_pp(xs[i], w, b, 1, 1, stale, i, 2)
             top, bot = _halo_rows(ops, dev, stale, i, 2)
             y = _conv(ops, dev, xs[i], w, b, 1, top, bot)
             _lib.device_status()
-            assert_close(y, ref, what=f"conv bn={bn} split={split} strip {i}")
+            assert_close(y, ref, what=f"conv bn={bn} split={split} pair={pair} strip {i}")
     finally:
         _lib.check(l.bxl_debug_force_tiles(0, 0, -1), l, kernels=0)
 

@@ -154,10 +154,12 @@ def test_auto_tiling_on_every_per_rank_linear_shape(tokens):
     _lib.device_status()
 
 
+@pytest.mark.parametrize("pair", [-1, 1])
 @pytest.mark.parametrize("M,K,F", [(300, 640, 2560), (2048, 1280, 5120), (64, 128, 512)])
-def test_gemm_with_fused_geglu(M, K, F):
+def test_gemm_with_fused_geglu(M, K, F, pair):
     dev = cuda_or_skip()
     _lib, ops = _ops()
+    l = _lib.lib()
     g = torch.Generator().manual_seed(M + F)
     x = h16(torch.randn(M, K, generator=g))
     w = h16(torch.randn(2 * F, K, generator=g) / K**0.5)
@@ -165,24 +167,34 @@ def test_gemm_with_fused_geglu(M, K, F):
     h = x @ w.t() + b
     ref = h[:, :F] * torch.nn.functional.gelu(h[:, F:])
     wi, bi = ops.geglu_interleave(w.half().to(dev), b.half().to(dev))
-    y = ops.gemm_geglu(x.half().to(dev), wi, bi)
-    _lib.device_status()
+    _lib.check(l.bxl_debug_force_tiles(0, 1 if pair == 1 else 0, pair), l, kernels=0)
+    try:
+        y = ops.gemm_geglu(x.half().to(dev), wi, bi)
+        _lib.device_status()
+    finally:
+        _lib.check(l.bxl_debug_force_tiles(0, 0, -1), l, kernels=0)
     assert y.shape == (M, F)
     assert_close(y, ref, what=f"gemm+geglu {M}x{K}x{F}")
 
 
+@pytest.mark.parametrize("pair", [-1, 1])
 @pytest.mark.parametrize("M,K,C", [(300, 640, 640), (2048, 1280, 1280), (512, 128, 128)])
-def test_gemm_with_two_destinations(M, K, C):
+def test_gemm_with_two_destinations(M, K, C, pair):
     """q | k|v projection in one launch, k|v into a wider (strided) destination."""
     dev = cuda_or_skip()
     _lib, ops = _ops()
+    l = _lib.lib()
     g = torch.Generator().manual_seed(M + C)
     x = h16(torch.randn(M, K, generator=g))
     w = h16(torch.randn(3 * C, K, generator=g) / K**0.5)
     ref = x @ w.t()
     slot = torch.zeros(M, 2 * C + 64, device=dev, dtype=torch.float16)
-    q, _ = ops.gemm_dual(x.half().to(dev), w.half().to(dev), C, out2=slot[:, : 2 * C])
-    _lib.device_status()
+    _lib.check(l.bxl_debug_force_tiles(0, 1 if pair == 1 else 0, pair), l, kernels=0)
+    try:
+        q, _ = ops.gemm_dual(x.half().to(dev), w.half().to(dev), C, out2=slot[:, : 2 * C])
+        _lib.device_status()
+    finally:
+        _lib.check(l.bxl_debug_force_tiles(0, 0, -1), l, kernels=0)
     assert_close(q, ref[:, :C], what="q part")
     assert_close(slot[:, : 2 * C], ref[:, C:], what="k|v part")
     assert float(slot[:, 2 * C :].abs().max()) == 0.0
@@ -192,7 +204,7 @@ def test_gemm_with_two_destinations(M, K, C):
 @pytest.mark.parametrize("M,K,N", [(300, 320, 384), (2048, 1280, 1280)])
 def test_cta_pair_tiles(M, K, N, bn):
     """256-row tiles computed by two CTAs with one MMA stream (cta_group::2), each CTA staging
-    half of the B tile.  Not selected by default; kept correct for the shapes it may serve."""
+    half of the B tile and reporting its copies to the leader's barrier."""
     dev = cuda_or_skip()
     _lib, ops = _ops()
     g = torch.Generator().manual_seed(M + bn)
