@@ -94,6 +94,31 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// One query row of a finished unit: read O (64 fp32 columns of this thread's TMEM lane),
+// normalise by the row sum and store 64 halves.  Kept out of line: it is called from inside the
+// K/V loop, where the registers are needed for the row of S.
+__device__ __noinline__ void attn_store_row(uint32_t o_addr, __half* dst, float inv_l) {
+  uint32_t o0[32], o1[32];
+  tmem_ld_32x32(o_addr, o0);
+  tmem_ld_32x32(o_addr + 32, o1);
+  tmem_ld_wait();
+  if (dst == nullptr) return;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint4 u0, u1;
+    u0.x = pack_f16x2(__uint_as_float(o0[8 * q]) * inv_l, __uint_as_float(o0[8 * q + 1]) * inv_l);
+    u0.y = pack_f16x2(__uint_as_float(o0[8 * q + 2]) * inv_l, __uint_as_float(o0[8 * q + 3]) * inv_l);
+    u0.z = pack_f16x2(__uint_as_float(o0[8 * q + 4]) * inv_l, __uint_as_float(o0[8 * q + 5]) * inv_l);
+    u0.w = pack_f16x2(__uint_as_float(o0[8 * q + 6]) * inv_l, __uint_as_float(o0[8 * q + 7]) * inv_l);
+    u1.x = pack_f16x2(__uint_as_float(o1[8 * q]) * inv_l, __uint_as_float(o1[8 * q + 1]) * inv_l);
+    u1.y = pack_f16x2(__uint_as_float(o1[8 * q + 2]) * inv_l, __uint_as_float(o1[8 * q + 3]) * inv_l);
+    u1.z = pack_f16x2(__uint_as_float(o1[8 * q + 4]) * inv_l, __uint_as_float(o1[8 * q + 5]) * inv_l);
+    u1.w = pack_f16x2(__uint_as_float(o1[8 * q + 6]) * inv_l, __uint_as_float(o1[8 * q + 7]) * inv_l);
+    *reinterpret_cast<uint4*>(dst + q * 8) = u0;
+    *reinterpret_cast<uint4*>(dst + 32 + q * 8) = u1;
+  }
+}
+
 __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -345,6 +370,24 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
     constexpr float kRaise = 8.f;  // raise m only when the tile maximum exceeds it by 2^8
     int cnt = 0;                   // K/V tiles this group has processed (all units)
     bool ok = true;
+    // The output of a finished unit stays in O_g while the first tile of the next unit is being
+    // exponentiated; it is read out and stored just before that tile's P is published (the P V
+    // product that would overwrite O_g is only issued after that).
+    int pend_w = -1;             // unit whose output is still in tensor memory
+    float pend_l = 1.f, pend_m = 0.f;
+    // wait for the last P V product of the pending unit (tile cnt - 1), then store / keep its rows
+    auto emit_pending = [&]() -> bool {
+      if (!mbar_wait(o_full(g), (cnt - 1) & 1u, abort_flag, p.dev_status, 602)) return false;
+      __syncwarp();
+      tc_fence_after_sync();
+      const int q_row = unit_q_row0(pend_w) + g * kTileQ + row;
+      __half* dst = (q_row < p.L_q) ? p.out + (long long)unit_img(pend_w) * p.out_img_stride + (long long)q_row * p.ld_out +
+                                          unit_head(pend_w) * kHeadDim
+                                    : nullptr;
+      attn_store_row(o_addr, dst, 1.f / pend_l);
+      pend_w = -1;
+      return true;
+    };
     for (int w = first_unit; w < units_total && ok; w += unit_step) {
       if (g >= unit_groups(w)) continue;
       float m_run = -INFINITY;   // running row maximum in the exp2 domain (score * scale * log2 e)
@@ -426,10 +469,14 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
           }
         }
         l_run = fmaf(l_run, alpha, (sum0 + sum1) + (sum2 + sum3));
-        // the previous tile's P V product must have finished: it read the P buffer, and O is only
-        // touched between two products (for the first tile of a unit this was awaited when the
-        // previous unit's output was read)
-        if (j > 0) {
+        // the previous P V product of this group must have finished: it read the P buffer, and O
+        // is only touched between two products
+        if (j == 0) {
+          if (pend_w >= 0 && !emit_pending()) {
+            ok = false;
+            break;
+          }
+        } else {
           if (!mbar_wait(o_full(g), (cnt - 1) & 1u, abort_flag, p.dev_status, 601)) {
             ok = false;
             break;
@@ -458,43 +505,24 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
         mbar_arrive(p_full(g));
       }
       if (!ok) break;
-      // ---- end of the unit: O_g is complete once the last P V product has finished ----
-      if (!mbar_wait(o_full(g), (cnt - 1) & 1u, abort_flag, p.dev_status, 602)) {
-        ok = false;
-        break;
-      }
-      __syncwarp();
-      tc_fence_after_sync();
-      uint32_t o0[32], o1[32];
-      tmem_ld_32x32(o_addr, o0);
-      tmem_ld_32x32(o_addr + 32, o1);
-      tmem_ld_wait();
-      if (S > 1) {
+      pend_w = w, pend_l = l_run, pend_m = m_run;
+    }
+    if (ok && pend_w >= 0) {
+      if (S == 1) {
+        emit_pending();
+      } else if (mbar_wait(o_full(g), (cnt - 1) & 1u, abort_flag, p.dev_status, 602)) {
+        // kv_split > 1: keep the partial result for the merge
+        __syncwarp();
+        tc_fence_after_sync();
+        uint32_t o0[32], o1[32];
+        tmem_ld_32x32(o_addr, o0);
+        tmem_ld_32x32(o_addr + 32, o1);
+        tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) fin_o[i] = o0[i], fin_o[32 + i] = o1[i];
-        fin_l = l_run;
-        fin_m = m_run;
+        fin_l = pend_l;
+        fin_m = pend_m;
         fin_valid = true;
-      } else {
-        const int q_row = unit_q_row0(w) + g * kTileQ + row;
-        if (q_row < p.L_q) {
-          const float inv_l = 1.f / l_run;
-          __half* dst = p.out + (long long)unit_img(w) * p.out_img_stride + (long long)q_row * p.ld_out + unit_head(w) * kHeadDim;
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 u0, u1;
-            u0.x = pack_f16x2(__uint_as_float(o0[8 * q]) * inv_l, __uint_as_float(o0[8 * q + 1]) * inv_l);
-            u0.y = pack_f16x2(__uint_as_float(o0[8 * q + 2]) * inv_l, __uint_as_float(o0[8 * q + 3]) * inv_l);
-            u0.z = pack_f16x2(__uint_as_float(o0[8 * q + 4]) * inv_l, __uint_as_float(o0[8 * q + 5]) * inv_l);
-            u0.w = pack_f16x2(__uint_as_float(o0[8 * q + 6]) * inv_l, __uint_as_float(o0[8 * q + 7]) * inv_l);
-            u1.x = pack_f16x2(__uint_as_float(o1[8 * q]) * inv_l, __uint_as_float(o1[8 * q + 1]) * inv_l);
-            u1.y = pack_f16x2(__uint_as_float(o1[8 * q + 2]) * inv_l, __uint_as_float(o1[8 * q + 3]) * inv_l);
-            u1.z = pack_f16x2(__uint_as_float(o1[8 * q + 4]) * inv_l, __uint_as_float(o1[8 * q + 5]) * inv_l);
-            u1.w = pack_f16x2(__uint_as_float(o1[8 * q + 6]) * inv_l, __uint_as_float(o1[8 * q + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(dst + q * 8) = u0;
-            *reinterpret_cast<uint4*>(dst + 32 + q * 8) = u1;
-          }
-        }
       }
     }
     // ---- kv_split > 1: merge the partial results of the cluster and write the output -------
