@@ -94,6 +94,51 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// Ragged last tile of a slot, one 32-column chunk with nv valid columns (warp-uniform): row
+// maximum, and P = exp2(s*sc - m) packed into pk[kOff .. kOff+15] with its sum.  Chunks without
+// a valid column cost nothing.
+__device__ __forceinline__ float ragged_chunk_max(const uint32_t (&v)[32], int nv) {
+  float m = -INFINITY;
+  if (nv >= 32) {
+    float m2 = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      m = max3(m, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+      m2 = max3(m2, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+    }
+    m = fmaxf(m, m2);
+  } else if (nv > 0) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < nv) m = fmaxf(m, __uint_as_float(v[i]));
+  }
+  return m;
+}
+template <int kOff>
+__device__ __forceinline__ float ragged_chunk_p(const uint32_t (&v)[32], uint32_t (&pk)[32], int nv, float sc, float m) {
+  float s0 = 0.f, s1 = 0.f;
+  if (nv >= 32) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float a = fast_exp2(fmaf(__uint_as_float(v[2 * i]), sc, -m)), b = fast_exp2(fmaf(__uint_as_float(v[2 * i + 1]), sc, -m));
+      s0 += a, s1 += b;
+      pk[kOff + i] = pack_f16x2(a, b);
+    }
+  } else if (nv > 0) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float a = (2 * i < nv) ? fast_exp2(fmaf(__uint_as_float(v[2 * i]), sc, -m)) : 0.f;
+      const float b = (2 * i + 1 < nv) ? fast_exp2(fmaf(__uint_as_float(v[2 * i + 1]), sc, -m)) : 0.f;
+      s0 += a, s1 += b;
+      pk[kOff + i] = pack_f16x2(a, b);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) pk[kOff + i] = 0u;
+  }
+  return s0 + s1;
+}
+
 // One query row of a finished unit: read O (64 fp32 columns of this thread's TMEM lane),
 // normalise by the row sum and store 64 halves.  Kept out of line: it is called from inside the
 // K/V loop, where the registers are needed for the row of S.
@@ -295,6 +340,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
       const bool has_next_unit = w_next < units_total;
       for (int j = 0; j < n_tiles && ok; ++j, ++kv_t) {
         const int st = kv_t % kKvStages;
+        // tokens of this tile that exist (the last tile of a slot may be ragged): P is zero beyond
+        // them, so their 16-token steps of the P V product are skipped
+        const int k_steps = (min(kTileKV, p.L_slot - ((tile0 + j) % tiles_per_slot) * kTileKV) + 15) / 16;
         // V tile [128 tokens][64] as stored: MN-major B operand, 8-token groups 1 KB apart
         const uint64_t vdesc = make_smem_desc_sw128(smem_base + AttnSmem::kV + st * 16384, 16, 1024);
         // the tile after this one in the stream
@@ -333,7 +381,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
 #pragma unroll
               for (int k = 0; k < kTileKV / 16; ++k) {
                 // tokens 16k..16k+15: 8 packed columns of P, V rows advance by 16 x 128 B
-                umma_f16_ts(d, pt + 8u * k, vdesc + 128u * k, idesc_o, acc | k);
+                if (k < k_steps) umma_f16_ts(d, pt + 8u * k, vdesc + 128u * k, idesc_o, acc | k);
               }
               umma_commit(o_full(g));
             }
@@ -423,14 +471,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
           }
           m_tile = fmaxf(fmaxf(ma, mb), fmaxf(mc, md));
         } else {
-          m_tile = -INFINITY;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (i < valid) m_tile = fmaxf(m_tile, __uint_as_float(v0[i]));
-            if (32 + i < valid) m_tile = fmaxf(m_tile, __uint_as_float(v1[i]));
-            if (64 + i < valid) m_tile = fmaxf(m_tile, __uint_as_float(v2[i]));
-            if (96 + i < valid) m_tile = fmaxf(m_tile, __uint_as_float(v3[i]));
-          }
+          m_tile = fmaxf(fmaxf(ragged_chunk_max(v0, valid), ragged_chunk_max(v1, valid - 32)),
+                         fmaxf(ragged_chunk_max(v2, valid - 64), ragged_chunk_max(v3, valid - 96)));
         }
         const float m_new = fmaxf(m_run, m_tile * sc);
         float alpha = 1.f;
@@ -457,16 +499,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
           }
         } else {
           // ragged last tile of a slot: columns >= valid contribute nothing
-          auto pexp = [&](uint32_t sv, int col) { return (col < valid) ? fast_exp2(fmaf(__uint_as_float(sv), sc, -m_run)) : 0.f; };
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float a0 = pexp(v0[2 * i], 2 * i), a1 = pexp(v0[2 * i + 1], 2 * i + 1);
-            const float b0 = pexp(v1[2 * i], 32 + 2 * i), b1 = pexp(v1[2 * i + 1], 33 + 2 * i);
-            const float c0 = pexp(v2[2 * i], 64 + 2 * i), c1 = pexp(v2[2 * i + 1], 65 + 2 * i);
-            const float d0 = pexp(v3[2 * i], 96 + 2 * i), d1 = pexp(v3[2 * i + 1], 97 + 2 * i);
-            sum0 += a0 + a1, sum1 += b0 + b1, sum2 += c0 + c1, sum3 += d0 + d1;
-            pa[i] = pack_f16x2(a0, a1), pa[16 + i] = pack_f16x2(b0, b1), pb[i] = pack_f16x2(c0, c1), pb[16 + i] = pack_f16x2(d0, d1);
-          }
+          sum0 = ragged_chunk_p<0>(v0, pa, valid, sc, m_run);
+          sum1 = ragged_chunk_p<16>(v1, pa, valid - 32, sc, m_run);
+          sum2 = ragged_chunk_p<0>(v2, pb, valid - 64, sc, m_run);
+          sum3 = ragged_chunk_p<16>(v3, pb, valid - 96, sc, m_run);
         }
         l_run = fmaf(l_run, alpha, (sum0 + sum1) + (sum2 + sum3));
         // the previous P V product of this group must have finished: it read the P buffer, and O
