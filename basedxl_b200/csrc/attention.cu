@@ -37,8 +37,8 @@
 namespace bxl {
 
 constexpr int kAttnThreads = 384;   // warps 0..7 softmax, 8 producer, 9 MMA issuer, 10..11 idle
-constexpr int kSoftmaxRegs = 216;   // registers per thread after the split: 8 x 32 x 216 + 4 x 32 x 72 = 64512
-constexpr int kOtherRegs = 72;
+constexpr int kSoftmaxRegs = 208;   // registers per thread after the split: 8 x 32 x 208 + 4 x 32 x 88 = 64512
+constexpr int kOtherRegs = 88;
 constexpr int kHeadDim = 64;
 constexpr int kTileQ = 128;
 constexpr int kTileKV = 128;
@@ -365,30 +365,64 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
           ok = false;
           break;
         }
-        for (int g = 0; g < 2 && ok; ++g) {
-          if (g < nxt_ng) ok = issue_s(nxt_qb, g, kv_t + 1);
-          if (g < ng && ok) {
-            // P_g of this tile is in tensor memory; O_g carries the right scale
-            if (!mbar_wait_warp(p_full(g), n_pv[g] & 1u, abort_flag, p.dev_status, 502)) {
+        // Four things are due for this tile: Q K^T of the next tile (per group, once the group
+        // has copied its S) and P V of this tile (per group, once its P is published).  They are
+        // issued in the order in which their conditions come true, so a late group never holds
+        // up the other one.
+        bool due_s[2] = {nxt_ng > 0, nxt_ng > 1};
+        bool due_pv[2] = {ng > 0, ng > 1};
+        const unsigned long long t_start = global_timer_ns();
+        uint32_t spins = 0;
+        while (due_s[0] || due_s[1] || due_pv[0] || due_pv[1]) {
+          bool progress = false;
+#pragma unroll
+          for (int g = 0; g < 2; ++g) {
+            if (due_s[g]) {
+              const bool ready = (n_s[g] == 0) || __all_sync(0xffffffffu, mbar_try_wait(s_free(g), (n_s[g] - 1) & 1u));
+              if (ready) {
+                ok = issue_s(nxt_qb, g, kv_t + 1);  // its own wait on s_free returns at once
+                due_s[g] = false, progress = true;
+              }
+            }
+            if (due_pv[g] && __all_sync(0xffffffffu, mbar_try_wait(p_full(g), n_pv[g] & 1u))) {
+              // P_g of this tile is in tensor memory; O_g carries the right scale
+              tc_fence_after_sync();
+              const uint32_t d = tmem_base + 256 + g * 64;
+              const uint32_t pt = tmem_base + 384 + g * 64;
+              const uint32_t acc = (j != 0);
+              if (leader) {
+#pragma unroll
+                for (int k = 0; k < kTileKV / 16; ++k) {
+                  // tokens 16k..16k+15: 8 packed columns of P, V rows advance by 16 x 128 B
+                  if (k < k_steps) umma_f16_ts(d, pt + 8u * k, vdesc + 128u * k, idesc_o, acc | k);
+                }
+                umma_commit(o_full(g));
+              }
+              __syncwarp();
+              ++n_pv[g];
+              due_pv[g] = false, progress = true;
+            }
+          }
+          if (!ok) break;
+          if (!progress && (++spins & 63u) == 0u) {
+            // bounded: give up after the common wait limit and report where
+            bool give_up = (*abort_flag != 0);
+            if (!give_up && global_timer_ns() - t_start > kWaitLimitNs) {
+              give_up = true;
+              *abort_flag = 1;
+              if (atomicCAS(&p.dev_status[0], kDevOk, kDevWaitTimeout) == kDevOk) {
+                p.dev_status[1] = 502;
+                p.dev_status[2] = static_cast<int>(blockIdx.x);
+              }
+              __threadfence();
+            }
+            if (__any_sync(0xffffffffu, give_up)) {
               ok = false;
               break;
             }
-            tc_fence_after_sync();
-            const uint32_t d = tmem_base + 256 + g * 64;
-            const uint32_t pt = tmem_base + 384 + g * 64;
-            const uint32_t acc = (j != 0);
-            if (leader) {
-#pragma unroll
-              for (int k = 0; k < kTileKV / 16; ++k) {
-                // tokens 16k..16k+15: 8 packed columns of P, V rows advance by 16 x 128 B
-                if (k < k_steps) umma_f16_ts(d, pt + 8u * k, vdesc + 128u * k, idesc_o, acc | k);
-              }
-              umma_commit(o_full(g));
-            }
-            __syncwarp();
-            ++n_pv[g];
           }
         }
+        if (!ok) break;
         // K and V of this tile are no longer needed once everything issued so far has completed
         if (ok) {
           if (leader) umma_commit(kv_empty(st));
