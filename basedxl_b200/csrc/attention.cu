@@ -5,31 +5,37 @@
 // slot: the own strip's fresh K/V and the peers' stale K/V are never
 // concatenated.  The same kernel serves cross-attention (one slot, 77 tokens).
 //
-// One CTA = 256 queries (two tiles of 128) of one (image, head).  320 threads:
-//   warp 0      TMA producer: both Q tiles once, then a ring of {K tile, V tile}
-//               (128 tokens x 64), shared by the two query tiles
-//   warp 1      tensor memory owner and tcgen05.mma issuer, alternating between
-//               the two query tiles g = 0, 1:
-//                 S_g     = Q_g K_j^T      (128x128, K-major operands)
-//                 Opart_g = P_g V_j        (128x64, V consumed MN-major as stored)
-//                 L_g     = P_g 1          (128x16: row sums of the rounded P)
-//               O_g and L_g accumulate in tensor memory over all K/V tiles.
-//   warps 2..5  softmax group 0, warps 6..9 softmax group 1: thread r owns query
-//               row r of its tile (= TMEM lane r).  Per K/V tile it reads its row of
-//               S once (128 registers), releases S at once so the next Q K^T can
-//               start, takes the row maximum, forms P = exp2(S*scale - m) two values
-//               per MUFU operation (ex2 on packed fp16, argument formed in fp32) and
-//               writes P to swizzled shared memory.  The running maximum m is only
-//               raised when the tile maximum exceeds it by more than 8 (a factor of
-//               256, harmless in fp16/fp32); only then O and L are rescaled in tensor
-//               memory (tcgen05.ld / multiply / tcgen05.st).  The result is exact:
-//               O and L always refer to the same m.
-// While one group runs its softmax the tensor core works for the other one.
+// Work unit = 256 queries (two tiles of 128) of one (image, head).  A CTA walks several units
+// (or, with a K/V split, a cluster of 2 or 4 CTAs shares one unit).  384 threads:
+//   warps 0..3  softmax group 0, warps 4..7 softmax group 1: thread r owns query row r of its
+//               tile (= TMEM lane r).  Per K/V tile it reads its row of S once (128 registers),
+//               releases S at once so the next Q K^T can start, takes the row maximum, forms
+//               P = exp2(S*scale - m) in fp32 (MUFU), sums the row in fp32 registers, packs P to
+//               fp16 and stores it to TENSOR MEMORY (tcgen05.st), from where the P V product
+//               reads it as its A operand: P never touches shared memory.  The running maximum
+//               m is only raised when the tile maximum exceeds it by more than 8 (a factor of
+//               256, harmless in fp16/fp32); only then O is rescaled in tensor memory
+//               (tcgen05.ld / multiply / tcgen05.st) and the row sum in its register.  The
+//               result is exact: O and the row sum always refer to the same m.
+//               These two warpgroups raise their register budget (setmaxnreg) at the expense
+//               of the third one.
+//   warp 8      TMA producer: the two Q tiles of a unit (double buffered across units), then a
+//               ring of {K tile, V tile} (128 tokens x 64) shared by the two query tiles
+//   warp 9      tensor memory owner and tcgen05.mma issuer (all 32 lanes run the loop, an
+//               elected lane issues), for the two query tiles g = 0, 1:
+//                 S_g  = Q_g K_j^T      (128x128, both operands K-major in shared memory)
+//                 O_g += P_g V_j        (128x64, P from tensor memory, V MN-major as stored)
+//               issued in the order in which their conditions come true.
+//   warps 10,11 idle (they complete the third warpgroup).
+// While one group runs its softmax the tensor core works for the other one; the K/V tiles of
+// all units of a CTA form one stream, so the first Q K^T of the next unit and the read-out of
+// the finished unit's output overlap the unit boundary.
 //
 // Roofline: tensor cores; algorithmic FLOPs = 4 * L_q * L_kv * 64 per (image, head).
-// With head dimension 64 the exponentials (one per score) cost as many issue
-// slots as the tensor core needs cycles, so ~50 % of tensor peak is the ceiling of
-// this formulation.
+// With head dimension 64 the softmax side (one MUFU exponential plus ~3 more instructions per
+// score, two warps per scheduler) needs more cycles per tile than the two matrix products;
+// measured, the kernel is bound by that instruction stream (evaluating part of the
+// exponentials with a polynomial on the FMA pipe made it slower).
 #include "bxl_common.cuh"
 #include "bxl_host.h"
 #include "../../include/basedxl_b200.h"
