@@ -582,7 +582,8 @@ static TileConfig choose_tiles(int tiles_m, int N, int num_kb, bool b_kn, int fo
         const double kb_unit = (num_kb + split - 1) / split;
         const double epi_us = 0.08 * (bn / 32.0) / split + (split > 1 ? 1.2 : 0.0);  // accumulator read-out (+ exchange)
         const double fill_us = 1.0 + (st < 4 ? 0.5 : 0.0) + (pair ? 0.3 : 0.0);       // pipeline ramp per unit
-        const double cost = rounds * (kb_unit * kb_us + epi_us) + fill_us + 3.0;
+        const double pair_tile_us = pair ? 0.45 : 0.0;  // accumulator hand-over between the two CTAs, per tile
+        const double cost = rounds * (kb_unit * kb_us + epi_us + pair_tile_us) + fill_us + 3.0;
         if (cost < best_cost - 1e-9) {
           best_cost = cost;
           best = TileConfig{bn, split, st, pair};
