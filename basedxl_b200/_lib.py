@@ -20,6 +20,7 @@ SIGNATURES = {
     "bxl_device_status": (_i, [C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
     "bxl_sm_count": (_i, []),
     "bxl_set_pdl": (_i, [_i]),
+    "bxl_set_static_weights": (_i, [_i]),
     "bxl_debug_force_tiles": (_i, [_i, _i, _i]),
     "bxl_debug_force_attn_split": (_i, [_i]),
     "bxl_gemm_f16": (_i, [_vp, _ll, _vp, _ll, _i, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _vp]),

@@ -51,6 +51,7 @@ struct alignas(64) GemmParams {
   int split;                   // K split over a cluster of `split` CTAs (1, 2 or 4)
   int pair;                    // CTA pairs (cta_group::2): 256-row tiles, each CTA stages half of B (split == 1)
   int stages;                  // depth of the operand ring
+  int b_static;                // B (weights) is not written by the preceding kernel: its copies start before the grid dependency wait
   // epilogue
   const __half* bias;          // [N] or null
   const __half* bias_rows;     // conv only: [B][N] per-image bias (time embedding) or null
@@ -223,7 +224,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
   if (S > 1 || kPair) cluster_sync_all();  // peers' barriers are initialised before anyone arrives on them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  pdl_wait();  // everything above overlaps the previous kernel's tail; global data from here on
+  // Everything above overlaps the previous kernel's tail; global data from here on.  With static
+  // weights the B producer does not wait: it fills the ring with B tiles while the previous
+  // kernel finishes (A, written by that kernel, is only loaded after the wait).
+  if (!(p.b_static && warp == 6)) pdl_wait();
 
   // ---- tile enumeration ------------------------------------------------------
   const int tiles_n = (p.N + BN - 1) / BN;
@@ -628,6 +632,7 @@ static int aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 1
 constexpr int kDefaultPair = -1;  // -1 = let the cost model decide
 constexpr double kConvAMinUs = 0.36;  // per-k-block floor of the convolution's image copies
 static int g_force_bn = 0, g_force_split = 0, g_force_pair = -1;
+static int g_static_b = 0;  // see bxl_set_static_weights
 
 }  // namespace bxl
 
@@ -673,7 +678,7 @@ extern "C" int bxl_gemm_f16(const void* A, long long lda, const void* B, long lo
     p.b_map[s] = p.b_map[0];
   }
   p.M = M, p.N = N, p.K = K, p.nseg = 1, p.b_kn = b_is_kn ? 1 : 0;
-  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair;
+  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair, p.b_static = g_static_b;
   p.bias = static_cast<const __half*>(bias);
   p.residual = static_cast<const __half*>(residual);
   p.ldr = ldr, p.C = C, p.ldc = ldc, p.out_f32 = out_f32 ? 1 : 0;
@@ -713,7 +718,7 @@ extern "C" int bxl_gemm_dual_f16(const void* A, long long lda, const void* B, lo
     p.b_map[s] = p.b_map[0];
   }
   p.M = M, p.N = N, p.K = K, p.nseg = 1, p.b_kn = 0;
-  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair;
+  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair, p.b_static = g_static_b;
   p.bias = static_cast<const __half*>(bias);
   p.C = C1, p.ldc = ldc1, p.C2 = C2, p.ldc2 = ldc2, p.n_split = n1;
   p.dev_status = st;
@@ -750,7 +755,7 @@ extern "C" int bxl_gemm_geglu_f16(const void* A, long long lda, const void* B, l
     p.b_map[s] = p.b_map[0];
   }
   p.M = M, p.N = N, p.K = K, p.nseg = 1, p.b_kn = 0;
-  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair;
+  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair, p.b_static = g_static_b;
   p.bias = static_cast<const __half*>(bias);
   p.C = C, p.ldc = ldc, p.out_f32 = 0, p.geglu = 1;
   p.dev_status = st;
@@ -826,6 +831,7 @@ extern "C" int bxl_gemm_split_f32(const float* A, const float* B, float* C, int 
     if (int rc = encode_tmap_f16(&p.b_map[i], bs[i], 2, bd, bstr, bbox)) return rc;
   }
   p.M = M, p.N = N, p.K = K, p.nseg = 3, p.b_kn = 1;
+  // b_static stays 0: the fp16 parts of B were written by the kernel launched just above
   p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair;
   p.C = C, p.ldc = N, p.out_f32 = 1;
   p.dev_status = st;
@@ -908,7 +914,7 @@ extern "C" int bxl_conv3x3_halo_f16(const void* x, long long x_img_stride, const
   p.b_map[1] = p.b_map[0];
   p.b_map[2] = p.b_map[0];
   p.M = B * H_out * W_out, p.N = C_out, p.K = K, p.nseg = 1, p.b_kn = 0;
-  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair;
+  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair, p.b_static = g_static_b;
   p.bias = static_cast<const __half*>(bias);
   p.bias_rows = static_cast<const __half*>(bias_rows);
   p.residual = static_cast<const __half*>(residual);
@@ -919,4 +925,9 @@ extern "C" int bxl_conv3x3_halo_f16(const void* x, long long x_img_stride, const
   p.has_top = top ? 1 : 0, p.has_bot = bot ? 1 : 0;
   p.dev_status = st;
   return launch<true>(p, B * tiles_x * tiles_y, (C_out + BN - 1) / BN, (cudaStream_t)stream);
+}
+
+extern "C" int bxl_set_static_weights(int enabled) {
+  g_static_b = enabled ? 1 : 0;
+  return kOk;
 }

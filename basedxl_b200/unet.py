@@ -204,6 +204,23 @@ class BasedXLUnet(BaseModel):
 
     # ------------------------------------------------------------------ one denoising step
     def forward(self, sample, timestep, encoder_hidden_states, added_cond_kwargs={}, **kwargs):
+        # Inside a UNet step the B operand of every GEMM and convolution is a model weight:
+        # the library may fetch it before a kernel waits for its predecessor.
+        self._static_weights(True)
+        try:
+            return self._forward(sample, timestep, encoder_hidden_states, added_cond_kwargs, **kwargs)
+        finally:
+            self._static_weights(False)
+
+    def _static_weights(self, on: bool):
+        if torch.device(self.basedxl_config.device).type != "cuda":
+            return
+        from . import _lib
+
+        l = _lib.lib()
+        _lib.check(l.bxl_set_static_weights(1 if on else 0), l, kernels=0)
+
+    def _forward(self, sample, timestep, encoder_hidden_states, added_cond_kwargs={}, **kwargs):
         torch.cuda.nvtx.range_push("unet::forward")
         cfg = self.basedxl_config
         b, c, h, w = sample.shape

@@ -45,6 +45,13 @@ int bxl_sm_count(void);
  * the environment, or this call with 0, turns it off.  No counterpart in the reference. */
 int bxl_set_pdl(int enabled);
 
+/* Promise that the B operand of the GEMM entry points and the packed weights of the
+ * convolution are never written by the kernel that precedes the launch on its stream (they
+ * are model weights).  Their copies then start before the kernel waits for its predecessor,
+ * which hides the first fetch from HBM behind the predecessor's tail.  Off by default; the
+ * UNet host turns it on.  No counterpart in the reference. */
+int bxl_set_static_weights(int enabled);
+
 /* Test hook: force the GEMM / convolution tile width (multiple of 32, <= 256), the K
  * split (1, 2 or 4) and CTA pairing (1 = 256-row tiles on two CTAs, 0 = off); 0 / 0 / -1
  * restore the built-in choice.  No counterpart in the reference. */

@@ -220,3 +220,28 @@ def test_cta_pair_tiles(M, K, N, bn):
     finally:
         _lib.check(l.bxl_debug_force_tiles(0, 0, -1), l, kernels=0)
     assert_close(y, ref, what=f"pair gemm bn={bn}")
+
+
+def test_static_weights_mode_chain():
+    """With the static-weights promise the B copies of a GEMM start before the kernel waits for
+    its predecessor; a chain in which every A is the previous output must still be exact."""
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    g = torch.Generator().manual_seed(11)
+    x = h16(torch.randn(512, 640, generator=g))
+    ws = [h16(torch.randn(640, 640, generator=g) / 640**0.5) for _ in range(4)]
+    ref = x
+    for w in ws:
+        ref = h16(ref @ w.t())
+    l = _lib.lib()
+    xd, wd = x.half().to(dev), [w.half().to(dev) for w in ws]
+    torch.cuda.synchronize()
+    _lib.check(l.bxl_set_static_weights(1), l, kernels=0)
+    try:
+        y = xd
+        for w in wd:
+            y = ops.gemm(y, w)
+        _lib.device_status()
+    finally:
+        _lib.check(l.bxl_set_static_weights(0), l, kernels=0)
+    assert_close(y, ref, what="gemm chain with static weights")
