@@ -31,6 +31,9 @@ def _ops():
         (1, 3, 200, 72, 4),       # ragged slots
         (2, 10, 512, 512, 8),     # benchmark shape at world size 8: L = 4096
         (2, 20, 256, 256, 4),     # 1280-level blocks, 4 strips
+        (2, 10, 4096, 77, 1),     # 320 units of 256 queries: every CTA walks two or three units
+        (2, 20, 1024, 256, 1),    # 160 units on 148 SMs: some CTAs walk two units of two tiles
+        (4, 20, 384, 100, 2),     # 160 units, every second one with a single query tile, ragged slots
     ],
 )
 def test_attention_core_vs_oracle(B, heads, Lq, Lslot, nslots):
