@@ -35,7 +35,7 @@ constexpr int kGemmThreads = 224;   // warp 0: A loads, warp 1: MMA, warps 2..5:
 constexpr int kMaxSeg = 3;
 constexpr int kABytes = kBM * kBK * 2;       // 16 KB
 constexpr int kSmemBudget = 227 * 1024;      // dynamic shared memory available to one CTA
-constexpr int kSmemMisc = 2048;              // alignment slack + barriers
+constexpr int kSmemMisc = 3072;              // alignment slack + barriers + the tile's bias row (256 floats)
 constexpr int kMaxStages = 8;
 
 struct alignas(64) GemmParams {
@@ -82,19 +82,33 @@ __host__ __device__ inline int recv_bytes(int bn, int split) { return split > 1 
 
 // Bias, per-image bias, residual, conversion and the global store of 32 consecutive
 // output columns [nb, nb+32) of one output row.
-template <bool kConv>
-__device__ __forceinline__ void store_chunk(const GemmParams& p, float (&f)[32], long long out_row, int nb, int img) {
-  const bool fullw = (nb + 32 <= p.N);
-  if (p.bias) {
+// Residual values of one full-width chunk (32 halves of this thread's output row), fetched a
+// chunk ahead of their use.
+struct ResidualChunk {
+  uint4 u[4];
+  bool valid;
+};
+__device__ __forceinline__ void load_residual(const GemmParams& p, long long out_row, int nb, ResidualChunk& r) {
+  r.valid = (p.residual != nullptr) && out_row >= 0 && (nb + 32 <= p.N);
+  if (r.valid) {
+    const __half* rr = p.residual + out_row * p.ldr + nb;
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (fullw || nb + j < p.N) f[j] += __half2float(p.bias[nb + j]);
+    for (int q = 0; q < 4; ++q) r.u[q] = *reinterpret_cast<const uint4*>(rr + q * 8);
   }
-  if (kConv && p.bias_rows) {
-    const __half* br = p.bias_rows + static_cast<long long>(img) * p.N;
+}
+
+// `sbias` = the tile's bias row in shared memory (bias + per-image bias, zero beyond N), indexed
+// from the tile's first column; `res` = this chunk's residual if it was prefetched.
+template <bool kConv>
+__device__ __forceinline__ void store_chunk(const GemmParams& p, float (&f)[32], long long out_row, int nb, int img,
+                                            const float* sbias, const ResidualChunk& res) {
+  const bool fullw = (nb + 32 <= p.N);
+  if (sbias) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (fullw || nb + j < p.N) f[j] += __half2float(br[nb + j]);
+    for (int q = 0; q < 8; ++q) {
+      const float4 b4 = *reinterpret_cast<const float4*>(sbias + 4 * q);
+      f[4 * q] += b4.x, f[4 * q + 1] += b4.y, f[4 * q + 2] += b4.z, f[4 * q + 3] += b4.w;
+    }
   }
   if (!kConv && p.geglu) {
     // columns arrive interleaved in groups of 16 values + 16 gates (weight rows were permuted by the
@@ -121,7 +135,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, float (&f)[32],
     if (fullw) {
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const uint4 u = *reinterpret_cast<const uint4*>(rr + q * 8);
+        const uint4 u = res.valid ? res.u[q] : *reinterpret_cast<const uint4*>(rr + q * 8);
         const __half2* h = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -187,6 +201,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
   uint8_t* misc = smem_gen + (bar_base - smem_base) + 256;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 8);
+  float* s_bias = reinterpret_cast<float*>(misc + 256);   // [256]: bias row of the tile in the epilogue
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5;
@@ -440,6 +455,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
         const int m = tm * kBM + row_in_tile;
         if (m < p.M) out_row = m;
       }
+      // Stage the tile's bias row while the MMAs of this tile are still running.  The four
+      // epilogue warps meet on named barrier 1 twice: nobody still reads the previous tile's
+      // row when it is overwritten, and the new row is complete before anybody reads it.
+      const bool has_bias = (p.bias != nullptr) || (kConv && p.bias_rows != nullptr);
+      if (has_bias) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int et = (warp - 2) * 32 + lane;   // 0..127
+        for (int j = et; j < BN; j += 128) {
+          float b = 0.f;
+          if (n0 + j < p.N) {
+            if (p.bias) b += __half2float(p.bias[n0 + j]);
+            if (kConv && p.bias_rows && img < p.cB) b += __half2float(p.bias_rows[static_cast<long long>(img) * p.N + n0 + j]);
+          }
+          s_bias[j] = b;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      ResidualChunk res_cur, res_next;
+      res_cur.valid = res_next.valid = false;
+      if (S == 1) load_residual(p, out_row, n0, res_cur);
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.dev_status, 300)) break;
       __syncwarp();
       tc_fence_after_sync();
@@ -449,14 +484,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
         for (int c = 0; c < chunks; ++c) {
           uint32_t v[32];
           tmem_ld_32x32(t_row + c * 32, v);
-          tmem_ld_wait();
           const int nb = n0 + c * 32;
+          // the next chunk's residual travels while this chunk is converted and stored
+          if (c + 1 < chunks) load_residual(p, out_row, nb + 32, res_next);
+          tmem_ld_wait();
           if (out_row >= 0 && nb < p.N) {
             float f[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-            store_chunk<kConv>(p, f, out_row, nb, img);
+            store_chunk<kConv>(p, f, out_row, nb, img, has_bias ? s_bias + c * 32 : nullptr, res_cur);
           }
+          res_cur = res_next;
+          res_next.valid = false;
         }
       } else {
         // ---- split-K: push the partial sums of the peers' column slices into their
@@ -502,7 +541,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
             }
           }
           const int nb = n0 + c * 32;
-          if (out_row >= 0 && nb < p.N) store_chunk<kConv>(p, f, out_row, nb, img);
+          if (out_row >= 0 && nb < p.N) store_chunk<kConv>(p, f, out_row, nb, img, has_bias ? s_bias + c * 32 : nullptr, res_cur);
         }
         // tell the peers their pushes have been consumed
         for (uint32_t o = 0; o < static_cast<uint32_t>(S); ++o)
