@@ -55,6 +55,9 @@ int sm_count() {
 }
 
 static int g_pdl = -1;
+static int g_static_weights = 0;
+bool static_weights() { return g_static_weights != 0; }
+void set_static_weights(bool on) { g_static_weights = on ? 1 : 0; }
 bool pdl_enabled() {
   if (g_pdl < 0) {
     const char* e = getenv("BXL_PDL");

@@ -32,6 +32,10 @@ int sm_count();
 // Whether kernels are launched with programmatic stream serialisation (default on;
 // BXL_PDL=0 in the environment or bxl_set_pdl(0) turns it off).
 bool pdl_enabled();
+// Whether weight operands (GEMM B, packed conv weights, LayerNorm scale/shift) may be fetched
+// before a kernel waits for its predecessor (bxl_set_static_weights).
+bool static_weights();
+void set_static_weights(bool on);
 
 // Launch through cudaLaunchKernelEx with the programmatic-serialisation attribute and
 // an optional thread-block cluster width.

@@ -167,12 +167,27 @@ __global__ void upsample2x_kernel(const uint4* __restrict__ x, uint4* __restrict
 
 // ---- LayerNorm over the last axis, one warp per row --------------------------------
 __global__ void layernorm_kernel(const __half* __restrict__ x, __half* __restrict__ y, const __half* __restrict__ gamma,
-                                 const __half* __restrict__ beta, long long rows, int C, float eps) {
+                                 const __half* __restrict__ beta, long long rows, int C, float eps, int w_static) {
   pdl_launch_dependents();
-  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x / 32;
   const int vecs = C / 8;
+  // scale and shift of this lane's columns; when they are model weights they are fetched while
+  // the previous kernel is still running
+  uint4 gu[6], bu[6];
+  auto load_affine = [&]() {
+#pragma unroll
+    for (int it = 0; it < 6; ++it) {
+      const int v = lane + 32 * it;
+      if (v < vecs) {
+        gu[it] = *reinterpret_cast<const uint4*>(gamma + v * 8);
+        bu[it] = *reinterpret_cast<const uint4*>(beta + v * 8);
+      }
+    }
+  };
+  if (w_static) load_affine();
+  pdl_wait();
+  if (!w_static) load_affine();
   for (long long r = blockIdx.x * (long long)wpb + (threadIdx.x >> 5); r < rows; r += (long long)gridDim.x * wpb) {
     const __half* xr = x + r * C;
     float vals[8 * 6];  // up to C = 1536: six 16-byte vectors per lane
@@ -215,10 +230,8 @@ __global__ void layernorm_kernel(const __half* __restrict__ x, __half* __restric
     for (int it = 0; it < 6; ++it) {
       const int v = lane + 32 * it;
       if (v < vecs) {
-        const uint4 gu = *reinterpret_cast<const uint4*>(gamma + v * 8);
-        const uint4 bu = *reinterpret_cast<const uint4*>(beta + v * 8);
-        const __half2* gh = reinterpret_cast<const __half2*>(&gu);
-        const __half2* bh = reinterpret_cast<const __half2*>(&bu);
+        const __half2* gh = reinterpret_cast<const __half2*>(&gu[it]);
+        const __half2* bh = reinterpret_cast<const __half2*>(&bu[it]);
         uint4 o;
         __half2* oh = reinterpret_cast<__half2*>(&o);
 #pragma unroll
@@ -356,7 +369,7 @@ extern "C" int bxl_layernorm_f16(const void* x, void* y, const void* gamma, cons
     return fail(kErrUnsupported, "bxl_layernorm_f16: C=%d must be a multiple of 8, at most 1536, pointers 16-byte aligned", C);
   return launch_kernel("layernorm_kernel launch", layernorm_kernel, dim3(grid_for(rows * 32, 256)), dim3(256), 0, (cudaStream_t)stream, 1,
                        static_cast<const __half*>(x), static_cast<__half*>(y), static_cast<const __half*>(gamma),
-                       static_cast<const __half*>(beta), rows, C, eps);
+                       static_cast<const __half*>(beta), rows, C, eps, static_weights() ? 1 : 0);
 }
 
 extern "C" int bxl_geglu_f16(const void* h, void* out, long long rows, int F, void* stream) {

@@ -520,7 +520,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
         }
         for (uint32_t o = 0; o < static_cast<uint32_t>(S); ++o)
           if (o != crank) mbar_arrive_remote(map_to_cta(recv_full_bar, o));
-        // own slice: wait for every peer's partials
+        // own slice: wait for every peer's partials (the first chunk's residual travels meanwhile)
+        load_residual(p, out_row, n0 + static_cast<int>(crank) * cps * 32, res_cur);
         if (!mbar_wait_cluster(recv_full_bar, it & 1u, abort_flag, p.dev_status, 302)) break;
         __syncwarp();
 #pragma unroll 1
@@ -528,6 +529,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
           const int c = crank * cps + cc;
           uint32_t v[32];
           tmem_ld_32x32(t_row + c * 32, v);
+          if (cc + 1 < cps) load_residual(p, out_row, n0 + (c + 1) * 32, res_next);
           tmem_ld_wait();
           float f[32];
 #pragma unroll
@@ -542,6 +544,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
           }
           const int nb = n0 + c * 32;
           if (out_row >= 0 && nb < p.N) store_chunk<kConv>(p, f, out_row, nb, img, has_bias ? s_bias + c * 32 : nullptr, res_cur);
+          res_cur = res_next;
+          res_next.valid = false;
         }
         // tell the peers their pushes have been consumed
         for (uint32_t o = 0; o < static_cast<uint32_t>(S); ++o)
@@ -671,7 +675,6 @@ static int aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 1
 constexpr int kDefaultPair = -1;  // -1 = let the cost model decide
 constexpr double kConvAMinUs = 0.36;  // per-k-block floor of the convolution's image copies
 static int g_force_bn = 0, g_force_split = 0, g_force_pair = -1;
-static int g_static_b = 0;  // see bxl_set_static_weights
 
 }  // namespace bxl
 
@@ -717,7 +720,7 @@ extern "C" int bxl_gemm_f16(const void* A, long long lda, const void* B, long lo
     p.b_map[s] = p.b_map[0];
   }
   p.M = M, p.N = N, p.K = K, p.nseg = 1, p.b_kn = b_is_kn ? 1 : 0;
-  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair, p.b_static = g_static_b;
+  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair, p.b_static = static_weights() ? 1 : 0;
   p.bias = static_cast<const __half*>(bias);
   p.residual = static_cast<const __half*>(residual);
   p.ldr = ldr, p.C = C, p.ldc = ldc, p.out_f32 = out_f32 ? 1 : 0;
@@ -757,7 +760,7 @@ extern "C" int bxl_gemm_dual_f16(const void* A, long long lda, const void* B, lo
     p.b_map[s] = p.b_map[0];
   }
   p.M = M, p.N = N, p.K = K, p.nseg = 1, p.b_kn = 0;
-  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair, p.b_static = g_static_b;
+  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair, p.b_static = static_weights() ? 1 : 0;
   p.bias = static_cast<const __half*>(bias);
   p.C = C1, p.ldc = ldc1, p.C2 = C2, p.ldc2 = ldc2, p.n_split = n1;
   p.dev_status = st;
@@ -794,7 +797,7 @@ extern "C" int bxl_gemm_geglu_f16(const void* A, long long lda, const void* B, l
     p.b_map[s] = p.b_map[0];
   }
   p.M = M, p.N = N, p.K = K, p.nseg = 1, p.b_kn = 0;
-  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair, p.b_static = g_static_b;
+  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair, p.b_static = static_weights() ? 1 : 0;
   p.bias = static_cast<const __half*>(bias);
   p.C = C, p.ldc = ldc, p.out_f32 = 0, p.geglu = 1;
   p.dev_status = st;
@@ -953,7 +956,7 @@ extern "C" int bxl_conv3x3_halo_f16(const void* x, long long x_img_stride, const
   p.b_map[1] = p.b_map[0];
   p.b_map[2] = p.b_map[0];
   p.M = B * H_out * W_out, p.N = C_out, p.K = K, p.nseg = 1, p.b_kn = 0;
-  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair, p.b_static = g_static_b;
+  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair, p.b_static = static_weights() ? 1 : 0;
   p.bias = static_cast<const __half*>(bias);
   p.bias_rows = static_cast<const __half*>(bias_rows);
   p.residual = static_cast<const __half*>(residual);
@@ -967,6 +970,6 @@ extern "C" int bxl_conv3x3_halo_f16(const void* x, long long x_img_stride, const
 }
 
 extern "C" int bxl_set_static_weights(int enabled) {
-  g_static_b = enabled ? 1 : 0;
+  set_static_weights(enabled != 0);
   return kOk;
 }
