@@ -286,6 +286,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
           y0 = (r / p.tiles_x) * p.th;
           x0 = (r % p.tiles_x) * p.tw;
         }
+        // position in the K loop, advanced without divisions: this thread's issue rate bounds the
+        // pipeline ramp of short K loops
+        const int cchunks = kConv ? p.cCin / kBK : 1;
+        int seg = kConv ? 0 : kb_begin / kb_per_seg;        // GEMM: operand segment and k-block inside it
+        int kk = kConv ? 0 : kb_begin % kb_per_seg;
+        int tap = kConv ? kb_begin / cchunks : 0;           // conv: filter tap (ky, kx) and channel chunk
+        int cc = kConv ? kb_begin % cchunks : 0;
+        int ky = tap / 3, kx = tap % 3;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.dev_status, loads_a ? 100 : 101)) {
             ok = false;
@@ -308,10 +316,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
           if (loads_a) {
             if (announces) mbar_arrive_expect_tx(full_bar(stage), kABytes * kWidth);
             if (kConv) {
-              const int cchunks = p.cCin / kBK;
-              const int tap = kb / cchunks;
-              const int c0 = (kb % cchunks) * kBK;
-              const int ky = tap / 3, kx = tap % 3;
+              const int c0 = cc * kBK;
               // input column of output column ox: stride*ox + kx - 1, addressed as
               // (parity, half-column) = ((kx-1) mod stride, ox + floor((kx-1)/stride))
               int par = 0, xoff = kx - 1;
@@ -336,17 +341,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
                 }
               }
             } else {
-              const int seg = kb / kb_per_seg;
-              const int k0 = (kb % kb_per_seg) * kBK;
-              load_2d(a_dst, &p.a_map[seg], k0, tm * kBM);
+              load_2d(a_dst, &p.a_map[seg], kk * kBK, tm * kBM);
             }
           } else {
             if (announces) mbar_arrive_expect_tx(full_bar(stage), b_rows * 128 * kWidth);
             if (kConv) {
               load_2d(b_dst, &p.b_map[0], kb * kBK, n0);
             } else {
-              const int seg = kb / kb_per_seg;
-              const int k0 = (kb % kb_per_seg) * kBK;
+              const int k0 = kk * kBK;
               if (p.b_kn) {
                 // B[K,N]: one 64(n) x 64(k) box per 64 output columns
                 for (int j = 0; j < b_rows / 64; ++j) load_2d(b_dst + j * 8192, &p.b_map[seg], n0 + j * 64, k0);
@@ -358,6 +360,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
           if (++stage == p.stages) {
             stage = 0;
             phase ^= 1u;
+          }
+          if (kConv) {
+            if (++cc == cchunks) {
+              cc = 0;
+              if (++kx == 3) kx = 0, ++ky;
+            }
+          } else if (++kk == kb_per_seg) {
+            kk = 0, ++seg;
           }
         }
       }
