@@ -29,7 +29,7 @@ SIGNATURES = {
     "bxl_gemm_split_workspace_bytes": (_ll, [_i, _i, _i]),
     "bxl_gemm_split_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _ll, _vp]),
     "bxl_conv_weight_pack_f16": (_i, [_vp, _vp, _i, _i, _vp]),
-    "bxl_conv3x3_halo_f16": (_i, [_vp, _ll, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "bxl_conv3x3_halo_f16": (_i, [_vp, _ll, _vp, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "bxl_conv3x3_direct_f16": (_i, [_vp, _ll, _vp, _vp, _ll, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "bxl_halo_pack_f16": (_i, [_vp, _ll, _vp, _i, _i, _i, _i, _i, _vp]),
     "bxl_groupnorm_scratch_bytes": (_ll, [_i, _i]),

@@ -55,6 +55,7 @@ struct alignas(64) GemmParams {
   // epilogue
   const __half* bias;          // [N] or null
   const __half* bias_rows;     // conv only: [B][N] per-image bias (time embedding) or null
+  long long ld_bias_rows;      // row stride of bias_rows in elements
   const __half* residual;      // [M][ldr] or null
   long long ldr;
   void* C;
@@ -476,7 +477,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
           float b = 0.f;
           if (n0 + j < p.N) {
             if (p.bias) b += __half2float(p.bias[n0 + j]);
-            if (kConv && p.bias_rows && img < p.cB) b += __half2float(p.bias_rows[static_cast<long long>(img) * p.N + n0 + j]);
+            if (kConv && p.bias_rows && img < p.cB) b += __half2float(p.bias_rows[static_cast<long long>(img) * p.ld_bias_rows + n0 + j]);
           }
           s_bias[j] = b;
         }
@@ -915,8 +916,8 @@ extern "C" int bxl_conv_weight_pack_f16(const void* w_oihw, void* w_packed, int 
 
 extern "C" int bxl_conv3x3_halo_f16(const void* x, long long x_img_stride, const void* top, const void* bot,
                                     long long halo_img_stride, const void* w_packed, const void* bias, const void* bias_rows,
-                                    const void* residual, void* y, int B, int C_in, int C_out, int H_in, int W, int stride,
-                                    void* stream) {
+                                    long long bias_rows_stride, const void* residual, void* y, int B, int C_in, int C_out,
+                                    int H_in, int W, int stride, void* stream) {
   if (!x || !w_packed || !y) return fail(kErrInvalidArg, "bxl_conv3x3_halo_f16: null operand");
   if (B <= 0 || H_in <= 0 || W <= 0) return fail(kErrInvalidArg, "bxl_conv3x3_halo_f16: non-positive extent");
   if (stride != 1 && stride != 2) return fail(kErrUnsupported, "bxl_conv3x3_halo_f16: stride %d (1 or 2 supported)", stride);
@@ -927,6 +928,8 @@ extern "C" int bxl_conv3x3_halo_f16(const void* x, long long x_img_stride, const
       (residual && !aligned16(residual)))
     return fail(kErrInvalidArg, "bxl_conv3x3_halo_f16: pointers must be 16-byte aligned");
   if (x_img_stride % 8 || halo_img_stride % 8) return fail(kErrInvalidArg, "bxl_conv3x3_halo_f16: image strides must be multiples of 8");
+  if (bias_rows && bias_rows_stride != 0 && bias_rows_stride < C_out)
+    return fail(kErrInvalidArg, "bxl_conv3x3_halo_f16: bias_rows_stride=%lld is smaller than C_out=%d", bias_rows_stride, C_out);
   int* st = device_status_ptr();
   if (!st) return fail(kErrCuda, "bxl_conv3x3_halo_f16: no device status word");
   GemmParams p;
@@ -969,6 +972,7 @@ extern "C" int bxl_conv3x3_halo_f16(const void* x, long long x_img_stride, const
   p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair, p.b_static = static_weights() ? 1 : 0;
   p.bias = static_cast<const __half*>(bias);
   p.bias_rows = static_cast<const __half*>(bias_rows);
+  p.ld_bias_rows = bias_rows_stride > 0 ? bias_rows_stride : C_out;
   p.residual = static_cast<const __half*>(residual);
   p.ldr = C_out, p.C = y, p.ldc = C_out, p.out_f32 = 0;
   p.cB = B, p.cHin = H_in, p.cW = W, p.cCin = C_in, p.cStride = stride, p.cHout = H_out, p.cWout = W_out;

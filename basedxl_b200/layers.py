@@ -173,3 +173,5 @@ class KernelLayers:
     linear_geglu = staticmethod(linear_geglu)
     upsample2x = staticmethod(upsample2x)
     memory_format = torch.channels_last
+    batched_time_projection = True   # all residual blocks' time-embedding projections in one GEMM
+    linear = staticmethod(lambda x, w, b=None: ops.linear(x, w, b))

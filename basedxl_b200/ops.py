@@ -173,14 +173,18 @@ def conv3x3(x, w_packed, bias=None, stride=1, top=None, bot=None, bias_rows=None
     _req(out.is_contiguous(), "conv3x3: output must be contiguous")
     if residual is not None:
         _req(residual.shape == out.shape and residual.is_contiguous(), "conv3x3: bad residual")
+    bias_rows_stride = 0
     if bias_rows is not None:
-        _req(bias_rows.shape == (B, Co) and bias_rows.is_contiguous(), "conv3x3: bias_rows must be [B,C_out]")
+        # [B, C_out], possibly a column slice of a wider matrix (rows bias_rows.stride(0) apart)
+        _req(bias_rows.shape == (B, Co) and bias_rows.stride(1) == 1 and bias_rows.dtype == torch.float16,
+             "conv3x3: bias_rows must be fp16 [B,C_out] with unit column stride")
+        bias_rows_stride = bias_rows.stride(0) if B > 1 else Co
     l = _lib.lib()
     if Ci % 64 == 0 and Co % 8 == 0:
         _lib.check(
             l.bxl_conv3x3_halo_f16(
-                _p(x), x.stride(0), _p(top), _p(bot), halo_stride, _p(w_packed), _p(bias), _p(bias_rows), _p(residual),
-                _p(out), B, Ci, Co, H, W, stride, _stream(),
+                _p(x), x.stride(0), _p(top), _p(bot), halo_stride, _p(w_packed), _p(bias), _p(bias_rows), bias_rows_stride,
+                _p(residual), _p(out), B, Ci, Co, H, W, stride, _stream(),
             ),
             l,
         )

@@ -113,14 +113,16 @@ int bxl_conv_weight_pack_f16(const void* w_oihw, void* w_packed, int c_out, int 
 /* 3x3 convolution, padding 1, stride 1 or 2, of an NHWC H-strip x[B,H_in,W,C_in]
  * whose missing rows above / below come from `top` / `bot` ([B,1,W,C_in], image
  * stride halo_img_stride; NULL = zero row, i.e. the image edge).  Output
- * y[B,H_in/stride,W/stride,C_out] (+ bias[C_out]) (+ bias_rows[B,C_out])
- * (+ residual, same shape as y).  Implicit GEMM on tcgen05; C_in % 64 == 0.
+ * y[B,H_in/stride,W/stride,C_out] (+ bias[C_out]) (+ bias_rows[B,C_out], rows
+ * bias_rows_stride elements apart, 0 = C_out: a slice of a wider matrix that holds the
+ * time-embedding projections of several layers) (+ residual, same shape as y).
+ * Implicit GEMM on tcgen05; C_in % 64 == 0.
  * Replaces: BasedConv2dPP.forward's padded-input assembly and F.conv2d
  * (basedxl/modules/conv2d.py:74-104) and naive_forward (:15-18). */
 int bxl_conv3x3_halo_f16(const void* x, long long x_img_stride, const void* top, const void* bot,
                          long long halo_img_stride, const void* w_packed, const void* bias, const void* bias_rows,
-                         const void* residual, void* y, int B, int C_in, int C_out, int H_in, int W, int stride,
-                         void* stream);
+                         long long bias_rows_stride, const void* residual, void* y, int B, int C_in, int C_out, int H_in,
+                         int W, int stride, void* stream);
 
 /* Same contract, stride 1, for the two thin convolutions at the ends of the
  * network (C_in <= 16, or C_out == 4): direct CUDA-core kernels.

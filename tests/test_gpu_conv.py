@@ -95,6 +95,12 @@ def test_conv_fused_epilogue():
     y = _conv(ops, dev, x, w, b, 1, None, None, bias_rows=temb.half().to(dev), residual=nhwc(res).half().to(dev))
     _lib.device_status()
     assert_close(y, ref, what="conv + per-image bias + residual")
+    # the per-image bias as a column slice of a wider matrix (all blocks' projections in one GEMM)
+    wide = torch.zeros(2, 512, dtype=torch.float16, device=dev)
+    wide[:, 128:320] = temb.half().to(dev)
+    y2 = _conv(ops, dev, x, w, b, 1, None, None, bias_rows=wide[:, 128:320], residual=nhwc(res).half().to(dev))
+    _lib.device_status()
+    assert torch.equal(y2, y)
 
 
 @pytest.mark.parametrize("tag", ["s1", "s2"])
