@@ -277,7 +277,13 @@ def run_b200_arm(args):
     # ---- device-resident loop -------------------------------------------------
     lat, ehs, added = pipe.prepare_inputs(**host)
     pipe.unet.reset()
-    pipe.denoise(lat, ehs, added, IMAGE_STEPS, 5.0, first_step=0, last_step=max(args.warmup, 1))  # untimed warm-up steps
+    # Untimed warm-up steps.  A patch-parallel run captures its second CUDA graph (the displaced
+    # step) at step warmup_steps + 1 of an image: the warm-up is extended to include that step, so
+    # that no graph capture falls into the timed region.
+    warm_steps = max(args.warmup, 1)
+    if not args.no_graph and cfg.n_device_per_batch > 1:
+        warm_steps = max(warm_steps, cfg.warmup_steps + 2)
+    pipe.denoise(lat, ehs, added, IMAGE_STEPS, 5.0, first_step=0, last_step=warm_steps)
     barrier()
     pipe.unet.reset()
     sampler = ClockSampler(dev.index if dev.index is not None else 0)
@@ -335,7 +341,8 @@ def run_b200_arm(args):
             "ms_per_step": round(ms_per_step, 3), "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"SDXL {args.height}x{args.width} UNet loop: latent 1x4x{args.height // 8}x{args.width // 8}, CFG batch 2, guidance 5.0, 50 Euler steps, 5 synchronous steps then displaced",
-                       "parallelism": par, "l2": "activations and weights per step (5 GB of fp16 weights) exceed L2; no explicit flush in the loop"},
+                       "parallelism": par, "l2": "activations and weights per step (5 GB of fp16 weights) exceed L2; no explicit flush in the loop",
+                       "warmup_steps_run": warm_steps},
             "clocks": clocks, "gpu_launches": launches, "cuda_graph": bool(pipe.unet.cuda_graph),
             "e2e": {"value": round(e2e_value, 4), "unit": UNIT, "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps},
             "roofline": roof,
