@@ -83,6 +83,14 @@ __host__ __device__ inline int recv_bytes(int bn, int split) { return split > 1 
 
 // Bias, per-image bias, residual, conversion and the global store of 32 consecutive
 // output columns [nb, nb+32) of one output row.
+// 32-byte store: one whole sector per instruction.
+__device__ __forceinline__ void st_global_v8(void* ptr, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t e, uint32_t f,
+                                             uint32_t g, uint32_t h) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(e),
+               "r"(f), "r"(g), "r"(h)
+               : "memory");
+}
+
 // Residual values of one full-width chunk (32 halves of this thread's output row), fetched a
 // chunk ahead of their use.
 struct ResidualChunk {
@@ -165,13 +173,19 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, float (&f)[32],
                      ? static_cast<__half*>(p.C2) + out_row * p.ldc2 + (nb - p.n_split)
                      : static_cast<__half*>(p.C) + out_row * p.ldc + nb;
     if (fullw) {
+      uint32_t w[16];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint4 u;
-        __half2* h = reinterpret_cast<__half2*>(&u);
+      for (int j = 0; j < 16; ++j) {
+        const __half2 h = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
+        w[j] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      if ((reinterpret_cast<uintptr_t>(cr) & 31u) == 0) {
+        // whole 32-byte sectors: a thread owns 64 contiguous bytes of its row
+        st_global_v8(cr, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
+        st_global_v8(cr + 16, w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]);
+      } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(f[q * 8 + 2 * j], f[q * 8 + 2 * j + 1]);
-        *reinterpret_cast<uint4*>(cr + q * 8) = u;
+        for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(cr + q * 8) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
       }
     } else {
       for (int j = 0; j < 32; ++j)
@@ -483,22 +497,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
       }
-      ResidualChunk res_cur, res_next;
-      res_cur.valid = res_next.valid = false;
-      if (S == 1) load_residual(p, out_row, n0, res_cur);
+      ResidualChunk res_cur, res_next, res_next2;
+      res_cur.valid = res_next.valid = res_next2.valid = false;
+      if (S == 1) {
+        // the residual of the first two chunks travels while the MMAs of this tile still run
+        load_residual(p, out_row, n0, res_cur);
+        if (BN > 32) load_residual(p, out_row, n0 + 32, res_next);
+      }
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.dev_status, 300)) break;
       __syncwarp();
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       if (S == 1) {
-#pragma unroll 1
-        for (int c = 0; c < chunks; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(t_row + c * 32, v);
+        // two chunks per trip: the accumulator load of the second is in flight while the first is
+        // converted and stored, and the residual is fetched two chunks ahead
+        auto emit = [&](const uint32_t (&v)[32], int c) {
           const int nb = n0 + c * 32;
-          // the next chunk's residual travels while this chunk is converted and stored
-          if (c + 1 < chunks) load_residual(p, out_row, nb + 32, res_next);
-          tmem_ld_wait();
           if (out_row >= 0 && nb < p.N) {
             float f[32];
 #pragma unroll
@@ -506,7 +520,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
             store_chunk<kConv>(p, f, out_row, nb, img, has_bias ? s_bias + c * 32 : nullptr, res_cur);
           }
           res_cur = res_next;
-          res_next.valid = false;
+          res_next = res_next2;
+          res_next2.valid = false;
+        };
+        uint32_t va[32], vb[32];
+        tmem_ld_32x32(t_row, va);
+#pragma unroll 1
+        for (int c = 0; c < chunks; c += 2) {
+          if (c + 2 < chunks) load_residual(p, out_row, n0 + (c + 2) * 32, res_next2);
+          tmem_ld_wait();
+          if (c + 1 < chunks) tmem_ld_32x32(t_row + (c + 1) * 32, vb);
+          emit(va, c);
+          if (c + 1 < chunks) {
+            if (c + 3 < chunks) load_residual(p, out_row, n0 + (c + 3) * 32, res_next2);
+            tmem_ld_wait();
+            if (c + 2 < chunks) tmem_ld_32x32(t_row + (c + 2) * 32, va);
+            emit(vb, c + 1);
+          }
         }
       } else {
         // ---- split-K: push the partial sums of the peers' column slices into their
