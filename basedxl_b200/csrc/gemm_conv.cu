@@ -10,14 +10,25 @@
 //   warp 1      allocates tensor memory and issues tcgen05.mma (one lane)
 //   warps 2..5  epilogue: tcgen05.ld the fp32 accumulator, add bias/residual,
 //               convert and store; runs while the next tile's mainloop fills the
-//               other accumulator buffer (two TMEM buffers of BN columns)
+//               other accumulator buffer (two TMEM buffers of BN columns).  Nothing
+//               the epilogue needs from global memory is fetched on its critical
+//               path: the tile's bias row is staged in shared memory while the MMAs
+//               still run, the residual is fetched two 32-column chunks ahead, the
+//               accumulator load of the next chunk is in flight during the current
+//               one, and a thread stores its 64 bytes of a chunk as two whole sectors.
 //
-// Tile width BN (32..256) and an optional K split are chosen per problem by the
-// host.  With a K split of S, the S CTAs of a thread-block cluster each run 1/S
-// of the K loop of the same tile and reduce through distributed shared memory:
-// every CTA owns BN/S output columns, receives the peers' fp32 partial sums for
-// them by remote shared-memory stores, adds its own accumulator and stores.  This
-// keeps all SMs busy when a strip's problem has only a handful of tiles.
+// Tile width BN (32..256), an optional K split and CTA pairing are chosen per
+// problem by the host.  With a K split of S, the S CTAs of a thread-block cluster
+// each run 1/S of the K loop of the same tile and reduce through distributed shared
+// memory: every CTA owns BN/S output columns, receives the peers' fp32 partial sums
+// for them by remote shared-memory stores, adds its own accumulator and stores.  This
+// keeps all SMs busy when a strip's problem has only a handful of tiles.  With
+// pairing, two CTAs form one 256-row tile (cta_group::2): each stages its own 128
+// rows of A and half of the B tile, every copy reports its bytes to the even CTA's
+// "full" barrier, and the even CTA issues the MMAs and frees the stage in both.
+//
+// With static weights (bxl_set_static_weights) the B producer does not wait for the
+// preceding kernel: weight tiles arrive while that kernel drains.
 //
 // Roofline: tensor cores.  Algorithmic FLOPs per tile = 2*128*BN*K.
 #include <math.h>
