@@ -154,19 +154,21 @@ __device__ __noinline__ void attn_store_row(uint32_t o_addr, __half* dst, float 
   tmem_ld_32x32(o_addr + 32, o1);
   tmem_ld_wait();
   if (dst == nullptr) return;
+  // 128 bytes of this thread's output row: four whole 32-byte sectors when the row is aligned
+  uint32_t w[32];
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    uint4 u0, u1;
-    u0.x = pack_f16x2(__uint_as_float(o0[8 * q]) * inv_l, __uint_as_float(o0[8 * q + 1]) * inv_l);
-    u0.y = pack_f16x2(__uint_as_float(o0[8 * q + 2]) * inv_l, __uint_as_float(o0[8 * q + 3]) * inv_l);
-    u0.z = pack_f16x2(__uint_as_float(o0[8 * q + 4]) * inv_l, __uint_as_float(o0[8 * q + 5]) * inv_l);
-    u0.w = pack_f16x2(__uint_as_float(o0[8 * q + 6]) * inv_l, __uint_as_float(o0[8 * q + 7]) * inv_l);
-    u1.x = pack_f16x2(__uint_as_float(o1[8 * q]) * inv_l, __uint_as_float(o1[8 * q + 1]) * inv_l);
-    u1.y = pack_f16x2(__uint_as_float(o1[8 * q + 2]) * inv_l, __uint_as_float(o1[8 * q + 3]) * inv_l);
-    u1.z = pack_f16x2(__uint_as_float(o1[8 * q + 4]) * inv_l, __uint_as_float(o1[8 * q + 5]) * inv_l);
-    u1.w = pack_f16x2(__uint_as_float(o1[8 * q + 6]) * inv_l, __uint_as_float(o1[8 * q + 7]) * inv_l);
-    *reinterpret_cast<uint4*>(dst + q * 8) = u0;
-    *reinterpret_cast<uint4*>(dst + 32 + q * 8) = u1;
+  for (int j = 0; j < 16; ++j) {
+    w[j] = pack_f16x2(__uint_as_float(o0[2 * j]) * inv_l, __uint_as_float(o0[2 * j + 1]) * inv_l);
+    w[16 + j] = pack_f16x2(__uint_as_float(o1[2 * j]) * inv_l, __uint_as_float(o1[2 * j + 1]) * inv_l);
+  }
+  if ((reinterpret_cast<uintptr_t>(dst) & 31u) == 0) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      st_global_v8(dst + q * 16, w[8 * q], w[8 * q + 1], w[8 * q + 2], w[8 * q + 3], w[8 * q + 4], w[8 * q + 5], w[8 * q + 6],
+                   w[8 * q + 7]);
+  } else {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(dst + q * 8) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
   }
 }
 

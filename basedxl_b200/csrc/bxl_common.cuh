@@ -109,6 +109,15 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
   return __all_sync(0xffffffffu, ok);
 }
 
+// 32-byte store: one whole sector per instruction.
+__device__ __forceinline__ void st_global_v8(void* ptr, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t e, uint32_t f,
+                                             uint32_t g, uint32_t h) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(e),
+               "r"(f), "r"(g), "r"(h)
+               : "memory");
+}
+
+
 // ---- thread-block clusters / distributed shared memory ------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;

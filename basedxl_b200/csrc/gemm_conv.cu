@@ -94,14 +94,6 @@ __host__ __device__ inline int recv_bytes(int bn, int split) { return split > 1 
 
 // Bias, per-image bias, residual, conversion and the global store of 32 consecutive
 // output columns [nb, nb+32) of one output row.
-// 32-byte store: one whole sector per instruction.
-__device__ __forceinline__ void st_global_v8(void* ptr, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t e, uint32_t f,
-                                             uint32_t g, uint32_t h) {
-  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(e),
-               "r"(f), "r"(g), "r"(h)
-               : "memory");
-}
-
 // Residual values of one full-width chunk (32 halves of this thread's output row), fetched a
 // chunk ahead of their use.
 struct ResidualChunk {
@@ -134,19 +126,21 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, float (&f)[32],
     // columns arrive interleaved in groups of 16 values + 16 gates (weight rows were permuted by the
     // caller); N is a multiple of 32 here, so the chunk is always complete
     __half* cr = static_cast<__half*>(p.C) + out_row * p.ldc + (nb >> 1);
+    uint32_t w[8];
 #pragma unroll
-    for (int q = 0; q < 2; ++q) {
-      uint4 u;
-      __half2* h = reinterpret_cast<__half2*>(&u);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int i = q * 8 + 2 * j;
-        const float g0 = f[16 + i], g1 = f[16 + i + 1];
-        const float y0 = f[i] * (0.5f * g0 * (1.f + erff(g0 * 0.70710678118654752f)));
-        const float y1 = f[i + 1] * (0.5f * g1 * (1.f + erff(g1 * 0.70710678118654752f)));
-        h[j] = __floats2half2_rn(y0, y1);
-      }
-      *reinterpret_cast<uint4*>(cr + q * 8) = u;
+    for (int j = 0; j < 8; ++j) {
+      const int i = 2 * j;
+      const float g0 = f[16 + i], g1 = f[16 + i + 1];
+      const float y0 = f[i] * (0.5f * g0 * (1.f + erff(g0 * 0.70710678118654752f)));
+      const float y1 = f[i + 1] * (0.5f * g1 * (1.f + erff(g1 * 0.70710678118654752f)));
+      const __half2 h = __floats2half2_rn(y0, y1);
+      w[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    if ((reinterpret_cast<uintptr_t>(cr) & 31u) == 0) {
+      st_global_v8(cr, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);  // the thread's 32 bytes: one whole sector
+    } else {
+      *reinterpret_cast<uint4*>(cr) = make_uint4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<uint4*>(cr + 8) = make_uint4(w[4], w[5], w[6], w[7]);
     }
     return;
   }
