@@ -39,3 +39,33 @@ def test_state_dicts_interchange_between_factories():
     b = UNet2DConditionModel(tiny_config(), layers=KernelLayers)
     missing, unexpected = b.load_state_dict(a.state_dict(), strict=True)
     assert not missing and not unexpected
+
+
+def test_batched_time_projection_equals_per_block_projection():
+    """One GEMM over the concatenated time-embedding projections of all residual blocks, each
+    block reading its column slice, gives the per-block result."""
+
+    class Batched(TorchLayers):
+        batched_time_projection = True
+        linear = staticmethod(lambda x, w, b=None: torch.nn.functional.linear(x, w, b))
+
+    torch.manual_seed(0)
+    cfg = tiny_config()
+    a = UNet2DConditionModel(cfg, layers=TorchLayers).eval()
+    b = UNet2DConditionModel(cfg, layers=Batched).eval()
+    b.load_state_dict(a.state_dict())
+    x = torch.randn(2, 4, 16, 16)
+    ehs = torch.randn(2, 7, cfg.cross_attention_dim)
+    added = {"text_embeds": torch.randn(2, 64), "time_ids": torch.tensor([[128.0, 128, 0, 0, 128, 128]] * 2)}
+    with torch.no_grad():
+        ya = a(x, torch.tensor(500.0), ehs, added_cond_kwargs=added)[0]
+        yb = b(x, torch.tensor(500.0), ehs, added_cond_kwargs=added)[0]
+        assert getattr(b, "_time_proj_cache", None) is not None  # the batched path ran
+        # a weight update invalidates the cached concatenation
+        first = next(m for m in b.modules() if hasattr(m, "time_emb_proj"))
+        first.time_emb_proj.bias.add_(1.0)
+        next(m for m in a.modules() if hasattr(m, "time_emb_proj")).time_emb_proj.bias.add_(1.0)
+        ya2 = a(x, torch.tensor(500.0), ehs, added_cond_kwargs=added)[0]
+        yb2 = b(x, torch.tensor(500.0), ehs, added_cond_kwargs=added)[0]
+    assert torch.allclose(ya, yb, rtol=1e-5, atol=1e-5)
+    assert torch.allclose(ya2, yb2, rtol=1e-5, atol=1e-5) and not torch.allclose(ya, ya2)
