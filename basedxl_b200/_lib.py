@@ -13,6 +13,19 @@ LIB_PATH = os.path.join(_PKG, "libbasedxl_b200.so")
 
 _vp, _ll, _i, _f = C.c_void_p, C.c_longlong, C.c_int, C.c_float
 
+
+
+class GemmFusedArgs(C.Structure):
+    """``bxl_gemm_fused_args`` of include/basedxl_b200.h."""
+
+    _fields_ = [
+        ("A", _vp), ("lda", _ll), ("B", _vp), ("ldb", _ll), ("bias", _vp), ("bias_f32", _vp), ("residual", _vp), ("ldr", _ll),
+        ("C", _vp), ("ldc", _ll), ("C2", _vp), ("ldc2", _ll), ("n_split", _i), ("geglu", _i),
+        ("ln_partials", _vp), ("ln_parts", _i), ("ln_colsum", _vp), ("ln_eps", _f),
+        ("row_stats", _vp), ("row_stats_capacity", _ll), ("M", _i), ("N", _i), ("K", _i),
+    ]
+
+
 # name -> (restype, argtypes); mirrors include/basedxl_b200.h one to one
 SIGNATURES = {
     "bxl_init": (_i, []),
@@ -26,6 +39,7 @@ SIGNATURES = {
     "bxl_gemm_f16": (_i, [_vp, _ll, _vp, _ll, _i, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _vp]),
     "bxl_gemm_dual_f16": (_i, [_vp, _ll, _vp, _ll, _vp, _vp, _ll, _i, _vp, _ll, _i, _i, _i, _vp]),
     "bxl_gemm_geglu_f16": (_i, [_vp, _ll, _vp, _ll, _vp, _vp, _ll, _i, _i, _i, _vp]),
+    "bxl_gemm_fused_f16": (_i, [C.POINTER(GemmFusedArgs), C.POINTER(_i), _vp]),
     "bxl_gemm_split_workspace_bytes": (_ll, [_i, _i, _i]),
     "bxl_gemm_split_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _ll, _vp]),
     "bxl_conv_weight_pack_f16": (_i, [_vp, _vp, _i, _i, _vp]),

@@ -79,6 +79,18 @@ struct alignas(64) GemmParams {
   long long ldc2;
   int n_split;
   int geglu;                   // epilogue pairs columns: out[16c+i] = h[32c+i] * gelu(h[32c+16+i]), N_out = N/2
+  // LayerNorm folded into this GEMM: A holds the UN-normalised rows and B the weights scaled by the
+  // LayerNorm gain; with mean_m / rstd_m of row m (from the partial sums its producer wrote) the
+  // epilogue forms rstd_m * (acc[m,n] - mean_m * colsum[n]) before bias and the rest.
+  const float2* ln_part;       // [M][ln_parts] partial (sum, sum of squares) of every row of A, or null
+  int ln_parts;
+  float ln_inv_k, ln_eps;      // 1 / row length, epsilon
+  const float* ln_colsum;      // [N]: sum over k of B[n,k]
+  const float* bias_f32;       // [N] fp32 bias, used instead of `bias` when set
+  // Row statistics of the fp16 output (for a LayerNorm folded into the NEXT GEMM): one partial
+  // (sum, sum of squares) per row and per column slice a CTA owns, [M][stat_parts].
+  float2* stat_out;
+  int stat_parts;
   // conv geometry
   int cB, cHin, cW, cCin, cStride, cHout, cWout;
   int tw, th;                  // tile = th rows x tw columns of output pixels (th*tw = 128)
@@ -111,10 +123,28 @@ __device__ __forceinline__ void load_residual(const GemmParams& p, long long out
 
 // `sbias` = the tile's bias row in shared memory (bias + per-image bias, zero beyond N), indexed
 // from the tile's first column; `res` = this chunk's residual if it was prefetched.
+// LayerNorm fold of one row: out = ln.a * acc + ln.b * colsum (a = rstd, b = -rstd * mean)
+struct LnRow {
+  float a, b;
+};
+// running (sum, sum of squares) of the fp16 values a thread has stored for its row
+struct RowStat {
+  float s, q;
+};
+
 template <bool kConv>
 __device__ __forceinline__ void store_chunk(const GemmParams& p, float (&f)[32], long long out_row, int nb, int img,
-                                            const float* sbias, const ResidualChunk& res) {
+                                            const float* sbias, const ResidualChunk& res, const float* scol, const LnRow& ln,
+                                            RowStat& st) {
   const bool fullw = (nb + 32 <= p.N);
+  if (!kConv && scol) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float4 c4 = *reinterpret_cast<const float4*>(scol + 4 * q);
+      f[4 * q] = fmaf(ln.a, f[4 * q], ln.b * c4.x), f[4 * q + 1] = fmaf(ln.a, f[4 * q + 1], ln.b * c4.y);
+      f[4 * q + 2] = fmaf(ln.a, f[4 * q + 2], ln.b * c4.z), f[4 * q + 3] = fmaf(ln.a, f[4 * q + 3], ln.b * c4.w);
+    }
+  }
   if (sbias) {
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
@@ -184,6 +214,15 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, float (&f)[32],
         const __half2 h = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
         w[j] = *reinterpret_cast<const uint32_t*>(&h);
       }
+      if (!kConv && p.stat_out) {
+        // statistics of the values as stored (rounded to fp16): what the next GEMM will read
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float2 g = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+          st.s += g.x + g.y;
+          st.q = fmaf(g.x, g.x, fmaf(g.y, g.y, st.q));
+        }
+      }
       if ((reinterpret_cast<uintptr_t>(cr) & 31u) == 0) {
         // whole 32-byte sectors: a thread owns 64 contiguous bytes of its row
         st_global_v8(cr, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
@@ -222,6 +261,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 8);
   float* s_bias = reinterpret_cast<float*>(misc + 256);   // [256]: bias row of the tile in the epilogue
+  float* s_colsum = s_bias + 256;                         // [256]: weight column sums (LayerNorm fold only; the host sizes the CTA for it)
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5;
@@ -488,20 +528,40 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
       // Stage the tile's bias row while the MMAs of this tile are still running.  The four
       // epilogue warps meet on named barrier 1 twice: nobody still reads the previous tile's
       // row when it is overwritten, and the new row is complete before anybody reads it.
-      const bool has_bias = (p.bias != nullptr) || (kConv && p.bias_rows != nullptr);
-      if (has_bias) {
+      const bool has_ln = !kConv && (p.ln_part != nullptr);
+      const bool has_bias = (p.bias != nullptr) || (p.bias_f32 != nullptr) || (kConv && p.bias_rows != nullptr);
+      if (has_bias || has_ln) {
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const int et = (warp - 2) * 32 + lane;   // 0..127
         for (int j = et; j < BN; j += 128) {
-          float b = 0.f;
+          float b = 0.f, cs = 0.f;
           if (n0 + j < p.N) {
-            if (p.bias) b += __half2float(p.bias[n0 + j]);
+            if (p.bias_f32) b += p.bias_f32[n0 + j];
+            else if (p.bias) b += __half2float(p.bias[n0 + j]);
             if (kConv && p.bias_rows && img < p.cB) b += __half2float(p.bias_rows[static_cast<long long>(img) * p.ld_bias_rows + n0 + j]);
+            if (has_ln) cs = p.ln_colsum[n0 + j];
           }
           s_bias[j] = b;
+          if (has_ln) s_colsum[j] = cs;
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
       }
+      // LayerNorm fold: this row's mean and reciprocal standard deviation from the partial sums
+      // the producer of A left (read while this tile's MMAs still run)
+      LnRow ln{1.f, 0.f};
+      if (has_ln && out_row >= 0) {
+        const float2* pp = p.ln_part + out_row * p.ln_parts;
+        float sm = 0.f, sq = 0.f;
+        for (int i = 0; i < p.ln_parts; ++i) {
+          const float2 v = pp[i];
+          sm += v.x, sq += v.y;
+        }
+        const float mean = sm * p.ln_inv_k;
+        const float var = fmaxf(sq * p.ln_inv_k - mean * mean, 0.f);
+        ln.a = rsqrtf(var + p.ln_eps);
+        ln.b = -ln.a * mean;
+      }
+      RowStat stat{0.f, 0.f};
       ResidualChunk res_cur, res_next, res_next2;
       res_cur.valid = res_next.valid = res_next2.valid = false;
       if (S == 1) {
@@ -522,7 +582,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
             float f[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-            store_chunk<kConv>(p, f, out_row, nb, img, has_bias ? s_bias + c * 32 : nullptr, res_cur);
+            store_chunk<kConv>(p, f, out_row, nb, img, has_bias ? s_bias + c * 32 : nullptr, res_cur,
+                               has_ln ? s_colsum + c * 32 : nullptr, ln, stat);
           }
           res_cur = res_next;
           res_next = res_next2;
@@ -589,7 +650,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
             }
           }
           const int nb = n0 + c * 32;
-          if (out_row >= 0 && nb < p.N) store_chunk<kConv>(p, f, out_row, nb, img, has_bias ? s_bias + c * 32 : nullptr, res_cur);
+          if (out_row >= 0 && nb < p.N)
+            store_chunk<kConv>(p, f, out_row, nb, img, has_bias ? s_bias + c * 32 : nullptr, res_cur,
+                               has_ln ? s_colsum + c * 32 : nullptr, ln, stat);
           res_cur = res_next;
           res_next.valid = false;
         }
@@ -597,6 +660,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
         for (uint32_t o = 0; o < static_cast<uint32_t>(S); ++o)
           if (o != crank) mbar_arrive_remote(map_to_cta(recv_free_bar, o));
       }
+      if (!kConv && p.stat_out && out_row >= 0)
+        p.stat_out[out_row * p.stat_parts + tn * S + (S > 1 ? static_cast<int>(crank) : 0)] = make_float2(stat.s, stat.q);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
@@ -633,9 +698,11 @@ struct TileConfig {
   int bn, split, stages, pair;
 };
 
-static int stages_for(int bn, int split, int pair = 0) {
+constexpr int kSmemLnExtra = 1024;           // the weight column-sum row of a GEMM with a folded LayerNorm
+
+static int stages_for(int bn, int split, int pair = 0, int extra_smem = 0) {
   const int stage = kABytes + (pair ? bn * 64 : bn * 128);
-  int st = (kSmemBudget - kSmemMisc - recv_bytes(bn, split)) / stage;
+  int st = (kSmemBudget - kSmemMisc - extra_smem - recv_bytes(bn, split)) / stage;
   if (st > kMaxStages) st = kMaxStages;
   return st;
 }
@@ -650,9 +717,9 @@ static int stages_for(int bn, int split, int pair = 0) {
 // convolution).  A wider tile or a pair moves fewer bytes per FLOP; a narrower tile or a K split
 // spreads the stream over more SMs when there are few tiles.
 static TileConfig choose_tiles(int tiles_m, int N, int num_kb, bool b_kn, int force_bn = 0, int force_split = 0,
-                               int force_pair = -1, double a_min_us = 0.0) {
+                               int force_pair = -1, double a_min_us = 0.0, int extra_smem = 0) {
   const int sms = sm_count();
-  TileConfig best{128, 1, stages_for(128, 1), 0};
+  TileConfig best{128, 1, stages_for(128, 1, 0, extra_smem), 0};
   double best_cost = 1e30;
   for (int pair = 0; pair <= 1; ++pair) {
     if (force_pair >= 0 && pair != force_pair) continue;
@@ -664,7 +731,7 @@ static TileConfig choose_tiles(int tiles_m, int N, int num_kb, bool b_kn, int fo
       for (int split = 1; split <= (pair ? 1 : 4); split *= 2) {
         if (force_split && split != force_split) continue;
         if ((bn / 32) % split || split > num_kb) continue;
-        const int st = stages_for(bn, split, pair);
+        const int st = stages_for(bn, split, pair, extra_smem);
         if (st < 3) continue;
         const int width = pair ? 2 : split;
         const int clusters = sms / width;
@@ -690,7 +757,8 @@ static TileConfig choose_tiles(int tiles_m, int N, int num_kb, bool b_kn, int fo
 template <bool kConv, bool kPair>
 static int launch_one(const GemmParams& p, int num_units, cudaStream_t stream) {
   const int b_rows = kPair ? p.bn / 2 : p.bn;
-  const int smem = p.stages * (kABytes + b_rows * 128) + recv_bytes(p.bn, kPair ? 1 : p.split) + kSmemMisc;
+  const int smem = p.stages * (kABytes + b_rows * 128) + recv_bytes(p.bn, kPair ? 1 : p.split) + kSmemMisc +
+                   (p.ln_part ? kSmemLnExtra : 0);
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -850,6 +918,81 @@ extern "C" int bxl_gemm_geglu_f16(const void* A, long long lda, const void* B, l
   return launch<false>(p, tiles_m, (N + tc.bn - 1) / tc.bn, (cudaStream_t)stream);
 }
 
+// General form of the three entry points above, plus a LayerNorm folded in on the input side and
+// per-row statistics on the output side.
+extern "C" int bxl_gemm_fused_f16(const bxl_gemm_fused_args* a, int* row_stats_parts, void* stream) {
+  if (!a) return fail(kErrInvalidArg, "bxl_gemm_fused_f16: null argument block");
+  const int M = a->M, N = a->N, K = a->K;
+  if (!a->A || !a->B || !a->C) return fail(kErrInvalidArg, "bxl_gemm_fused_f16: null operand");
+  if (M <= 0 || N <= 0 || K <= 0) return fail(kErrInvalidArg, "bxl_gemm_fused_f16: non-positive extent M=%d N=%d K=%d", M, N, K);
+  if (a->lda % 8 || a->ldb % 8 || a->lda < K || a->ldb < K) return fail(kErrInvalidArg, "bxl_gemm_fused_f16: bad lda/ldb");
+  if (!aligned16(a->A) || !aligned16(a->B) || !aligned16(a->C) || (a->residual && !aligned16(a->residual)) || (a->C2 && !aligned16(a->C2)))
+    return fail(kErrInvalidArg, "bxl_gemm_fused_f16: operands must be 16-byte aligned");
+  if (a->geglu && (N % 32 || a->n_split || a->residual || a->row_stats))
+    return fail(kErrInvalidArg, "bxl_gemm_fused_f16: the GEGLU epilogue needs N %% 32 == 0 and excludes a second destination, a residual and row statistics");
+  const int n_out = a->geglu ? N / 2 : N;
+  if (a->n_split) {
+    if (!a->C2 || a->n_split <= 0 || a->n_split >= N || a->n_split % 32 || N % 8 || a->residual || a->row_stats)
+      return fail(kErrInvalidArg, "bxl_gemm_fused_f16: second destination needs 0 < n_split < N, n_split %% 32 == 0, no residual, no row statistics");
+    if (a->ldc % 8 || a->ldc2 % 8 || a->ldc < a->n_split || a->ldc2 < N - a->n_split) return fail(kErrInvalidArg, "bxl_gemm_fused_f16: bad ldc/ldc2");
+  } else if (a->ldc % 8 || a->ldc < n_out) {
+    return fail(kErrInvalidArg, "bxl_gemm_fused_f16: bad ldc");
+  }
+  if (a->residual && (a->ldr % 8 || a->ldr < N)) return fail(kErrInvalidArg, "bxl_gemm_fused_f16: bad ldr");
+  const bool ln = a->ln_partials != nullptr;
+  if (ln && (a->ln_parts <= 0 || !a->ln_colsum || !(a->ln_eps > 0.f) || (reinterpret_cast<uintptr_t>(a->ln_partials) & 7u)))
+    return fail(kErrInvalidArg, "bxl_gemm_fused_f16: folded LayerNorm needs ln_parts > 0, column sums and a positive epsilon");
+  if (a->row_stats && (N % 32 || !row_stats_parts || (reinterpret_cast<uintptr_t>(a->row_stats) & 7u)))
+    return fail(kErrInvalidArg, "bxl_gemm_fused_f16: row statistics need N %% 32 == 0 and a place for the partial count");
+  int* st = device_status_ptr();
+  if (!st) return fail(kErrCuda, "bxl_gemm_fused_f16: no device status word");
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  const int tiles_m = (M + kBM - 1) / kBM;
+  const TileConfig tc = choose_tiles(tiles_m, N, (K + kBK - 1) / kBK, false, g_force_bn, g_force_split,
+                                     g_force_pair < 0 ? kDefaultPair : g_force_pair, 0.0, ln ? kSmemLnExtra : 0);
+  const int tiles_n = (N + tc.bn - 1) / tc.bn;
+  if (a->row_stats) {
+    const long long parts = (long long)tiles_n * (tc.pair ? 1 : tc.split);
+    if (a->row_stats_capacity < 2ll * M * parts)
+      return fail(kErrTooLarge, "bxl_gemm_fused_f16: row statistics need %lld floats, %lld given", 2ll * M * parts, a->row_stats_capacity);
+    *row_stats_parts = (int)parts;
+    p.stat_out = reinterpret_cast<float2*>(a->row_stats);
+    p.stat_parts = (int)parts;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    uint64_t str[1] = {(uint64_t)a->lda * 2};
+    uint32_t box[2] = {kBK, kBM};
+    if (int rc = encode_tmap_f16(&p.a_map[0], a->A, 2, dims, str, box)) return rc;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+    uint64_t str[1] = {(uint64_t)a->ldb * 2};
+    uint32_t box[2] = {kBK, (uint32_t)(tc.pair ? tc.bn / 2 : tc.bn)};
+    if (int rc = encode_tmap_f16(&p.b_map[0], a->B, 2, dims, str, box)) return rc;
+  }
+  for (int s = 1; s < kMaxSeg; ++s) {
+    p.a_map[s] = p.a_map[0];
+    p.b_map[s] = p.b_map[0];
+  }
+  p.M = M, p.N = N, p.K = K, p.nseg = 1, p.b_kn = 0;
+  p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair, p.b_static = static_weights() ? 1 : 0;
+  p.bias = static_cast<const __half*>(a->bias);
+  p.bias_f32 = a->bias_f32;
+  p.residual = static_cast<const __half*>(a->residual);
+  p.ldr = a->ldr, p.C = a->C, p.ldc = a->ldc, p.C2 = a->C2, p.ldc2 = a->ldc2, p.n_split = a->n_split, p.geglu = a->geglu ? 1 : 0;
+  if (ln) {
+    p.ln_part = reinterpret_cast<const float2*>(a->ln_partials);
+    p.ln_parts = a->ln_parts;
+    p.ln_inv_k = 1.f / (float)K;
+    p.ln_eps = a->ln_eps;
+    p.ln_colsum = a->ln_colsum;
+  }
+  p.dev_status = st;
+  return launch<false>(p, tiles_m, tiles_n, (cudaStream_t)stream);
+}
+
 extern "C" int bxl_debug_force_tiles(int bn, int split, int pair) {
   if (bn < 0 || bn > 256 || bn % 32 || (split != 0 && split != 1 && split != 2 && split != 4) || pair < -1 || pair > 1)
     return fail(kErrInvalidArg, "bxl_debug_force_tiles: bn must be 0 or a multiple of 32 up to 256, split 0, 1, 2 or 4, pair -1, 0 or 1");
@@ -930,7 +1073,9 @@ extern "C" int bxl_gemm_split_f32(const float* A, const float* B, float* C, int 
 namespace bxl {
 // [C_out][C_in][3][3] -> [C_out][ky][kx][C_in]  (K index = tap*C_in + c)
 __global__ void conv_weight_pack_kernel(const __half* __restrict__ w, __half* __restrict__ out, int cout, int cin) {
-  pdl_launch_dependents();
+  // No early release of the successor: a convolution launched right after this kernel may fetch
+  // the packed weights before its own grid-dependency wait (static-weights mode), so it must not
+  // start before every store below has completed.
   pdl_wait();
   const long long total = (long long)cout * cin * 9;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {

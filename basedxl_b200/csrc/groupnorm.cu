@@ -43,13 +43,11 @@ __global__ void __launch_bounds__(512) groupnorm_stats_kernel(const __half* __re
                                                               int* __restrict__ ticket, float* __restrict__ moments, int B) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float s_ch[];  // [2][C] per-channel sum / sum of squares
+  extern __shared__ float s_part[];  // [rows][2][C]: every thread's channel sums / sums of squares, no atomics
   __shared__ int s_last;
   const int vecs = C / 8;               // 16-byte vectors per pixel
   const int rows = blockDim.x / vecs;   // pixels handled per sweep
   const int part = blockIdx.x, img = blockIdx.y;
-  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) s_ch[i] = 0.f;
-  __syncthreads();
   const int v = threadIdx.x % vecs, r = threadIdx.x / vecs;
   float s1[8], s2[8];
 #pragma unroll
@@ -69,19 +67,32 @@ __global__ void __launch_bounds__(512) groupnorm_stats_kernel(const __half* __re
       accumulate(u0), accumulate(u1), accumulate(u2), accumulate(u3);
     }
     for (; pix < p1; pix += rows) accumulate(__ldg(reinterpret_cast<const uint4*>(base + (long long)pix * C)));
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      atomicAdd(&s_ch[v * 8 + j], s1[j]);
-      atomicAdd(&s_ch[C + v * 8 + j], s2[j]);
-    }
+    float* d1 = s_part + ((long long)r * 2) * C + v * 8;
+    float* d2 = d1 + C;
+    *reinterpret_cast<float4*>(d1) = make_float4(s1[0], s1[1], s1[2], s1[3]);
+    *reinterpret_cast<float4*>(d1 + 4) = make_float4(s1[4], s1[5], s1[6], s1[7]);
+    *reinterpret_cast<float4*>(d2) = make_float4(s2[0], s2[1], s2[2], s2[3]);
+    *reinterpret_cast<float4*>(d2 + 4) = make_float4(s2[4], s2[5], s2[6], s2[7]);
   }
   __syncthreads();
+  // one warp per (group, moment): lanes stride over the rows x channels-of-the-group sums, then a
+  // shuffle tree - a fixed summation order, so the result does not depend on scheduling
   const int cpg = C / G;
-  if (threadIdx.x < 2 * G) {
-    const int g = threadIdx.x % G, which = threadIdx.x / G;
-    float acc = 0.f;
-    for (int c = 0; c < cpg; ++c) acc += s_ch[which * C + g * cpg + c];
-    partials[(((long long)img * parts + part) * G + g) * 2 + which] = acc;
+  {
+    const int lane_ = threadIdx.x & 31, warp_ = threadIdx.x >> 5, warps_ = blockDim.x >> 5;
+    if (warp_ < warps_) {
+      for (int i = warp_; i < 2 * G; i += warps_) {
+        const int g = i % G, which = i / G;
+        float acc = 0.f;
+        for (int e = lane_; e < rows * cpg; e += 32) {
+          const int rr = e / cpg, c = e - rr * cpg;
+          acc += s_part[((long long)rr * 2 + which) * C + g * cpg + c];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane_ == 0) partials[(((long long)img * parts + part) * G + g) * 2 + which] = acc;
+      }
+    }
   }
   // last CTA of the whole grid folds the partials
   __threadfence();
@@ -207,6 +218,9 @@ static int gn_threads(int C) {
   return vecs * k;
 }
 
+// per-thread partial sums of the statistics kernel: [rows][2][C] floats (at most 32 KB)
+static size_t gn_stats_smem(int C) { return (size_t)(gn_threads(C) / (C / 8)) * 2 * C * sizeof(float); }
+
 static int gn_parts(int HW, int C, int B) {
   const int rows = gn_threads(C) / (C / 8);
   int parts = (HW + rows * 16 - 1) / (rows * 16);  // >= 16 pixels per thread: the per-CTA fold is amortised
@@ -243,7 +257,7 @@ extern "C" int bxl_groupnorm_stats_f16(const void* x, long long img_stride, int 
   const int threads = gn_threads(C), parts = gn_parts(HW, C, B);
   int* ticket = static_cast<int*>(scratch);
   float* partials = reinterpret_cast<float*>(static_cast<char*>(scratch) + 256);
-  return launch_kernel("groupnorm_stats_kernel launch", groupnorm_stats_kernel, dim3(parts, B), dim3(threads), 2 * C * sizeof(float),
+  return launch_kernel("groupnorm_stats_kernel launch", groupnorm_stats_kernel, dim3(parts, B), dim3(threads), gn_stats_smem(C),
                        (cudaStream_t)stream, 1, static_cast<const __half*>(x), img_stride, HW, C, G, parts, partials, ticket,
                        moments, B);
 }
@@ -314,7 +328,7 @@ extern "C" int bxl_groupnorm_stats_noalloc_f16(const void* x, long long img_stri
   // the ticket word must start at zero whatever an earlier call left behind
   if (int rc = check_cuda(cudaMemsetAsync(scratch, 0, 256, s), "clear ticket")) return rc;
   const int threads = gn_threads(C), parts = gn_parts(HW, C, B);
-  groupnorm_stats_kernel<<<dim3(parts, B), threads, 2 * C * sizeof(float), s>>>(
+  groupnorm_stats_kernel<<<dim3(parts, B), threads, gn_stats_smem(C), s>>>(
       static_cast<const __half*>(x), img_stride, HW, C, G, parts, reinterpret_cast<float*>(scratch + 256),
       reinterpret_cast<int*>(scratch), moments, B);
   return check_cuda(cudaGetLastError(), "groupnorm_stats_kernel launch (static scratch)");

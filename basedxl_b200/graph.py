@@ -31,6 +31,9 @@ class GraphedStep:
         self.static = None
         self.out = None
         self._cond_key = None
+        # the conditioning tensors the key was taken from: holding them keeps their storage from
+        # being handed to a different tensor (same address, version 0) that would match the key
+        self._cond_ref = None
         self.kernels_per_replay = 0  # library kernels recorded in the graph
         self.replays = 0
 
@@ -43,6 +46,8 @@ class GraphedStep:
             self.graph = None
         self.out = None
         self.static = None
+        self._cond_key = None
+        self._cond_ref = None
 
     def _cond_id(self, ehs, added):
         return (ehs.data_ptr(), ehs._version) + tuple((v.data_ptr(), v._version) for v in added.values())
@@ -56,6 +61,7 @@ class GraphedStep:
                 "added": {k: v.clone() for k, v in added.items()},
             }
             self._cond_key = self._cond_id(ehs, added)
+            self._cond_ref = (ehs, dict(added))
             s = self.static
             if self.on_condition_change is not None:
                 self.on_condition_change(s["sample"], s["timestep"], s["ehs"], s["added"])
@@ -84,6 +90,7 @@ class GraphedStep:
                 for k, v in added.items():
                     s["added"][k].copy_(v)
                 self._cond_key = key
+                self._cond_ref = (ehs, dict(added))
                 if self.on_condition_change is not None:
                     self.on_condition_change(s["sample"], s["timestep"], s["ehs"], s["added"])
         self.graph.replay()

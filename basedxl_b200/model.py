@@ -116,8 +116,11 @@ class BasedXLPipeline:
         guidance_scale: float = 5.0,
         latents: torch.Tensor | None = None,
         generator: torch.Generator | None = None,
+        last_step: int | None = None,
         **kwargs,
     ):
+        """One image.  ``last_step`` (not in the reference) stops after that many steps of the
+        ``num_inference_steps``-step schedule and returns the latents reached."""
         cfg = self.basedxl_config
         assert "width" not in kwargs or cfg.width == kwargs["width"]
         assert "height" not in kwargs or cfg.height == kwargs["height"]
@@ -125,5 +128,5 @@ class BasedXLPipeline:
         lat, ehs, added = self.prepare_inputs(
             prompt_embeds, pooled_prompt_embeds, negative_prompt_embeds, negative_pooled_prompt_embeds, latents, generator
         )
-        lat = self.denoise(lat, ehs, added, num_inference_steps, guidance_scale)
+        lat = self.denoise(lat, ehs, added, num_inference_steps, guidance_scale, last_step=last_step)
         return PipelineOutput(lat)

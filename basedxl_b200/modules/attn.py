@@ -87,14 +87,19 @@ def _lin(layer: nn.Module, x: torch.Tensor, residual=None, out=None) -> torch.Te
 
 
 def _finish(attn, o: torch.Tensor, hidden_in: torch.Tensor, residual) -> torch.Tensor:
-    """to_out projection (+ fused residual), then the module's own residual /
-    rescale options (basedxl/modules/attn.py:158-166)."""
-    y = _lin(attn.to_out[0], o, residual=residual)
+    """to_out projection, then the module's own residual / rescale options
+    (basedxl/modules/attn.py:158-166), then the transformer block's outer residual.  The outer
+    residual rides in the projection's epilogue only when the module's options leave the
+    projection's result untouched; otherwise it is added after them, as the block would."""
+    plain = not attn.residual_connection and attn.rescale_output_factor == 1.0
+    y = _lin(attn.to_out[0], o, residual=residual if plain else None)
     # to_out[1] is a Dropout; inference only
     if attn.residual_connection:
         y = y + hidden_in
     if attn.rescale_output_factor != 1.0:
         y = y / attn.rescale_output_factor
+    if residual is not None and not plain:
+        y = y + residual
     return y
 
 

@@ -116,6 +116,96 @@ def gemm_geglu(a, w_interleaved, bias_interleaved=None, out=None):
     return out
 
 
+class RowStats:
+    """Per-row partial sums (sum, sum of squares) of a matrix a GEMM has just written:
+    ``buf[m, part, 2]`` fp32 with ``parts`` partials per row.  Input of a LayerNorm folded into
+    the next GEMM."""
+
+    __slots__ = ("buf", "parts")
+
+    def __init__(self, buf: torch.Tensor, parts: int):
+        self.buf, self.parts = buf, parts
+
+    def moments(self, k: int):
+        """(mean, variance) per row, for checking."""
+        s = self.buf[:, : self.parts].sum(dim=1)
+        mean = s[:, 0] / k
+        return mean, s[:, 1] / k - mean * mean
+
+
+class FoldedLayerNorm:
+    """What a GEMM needs to apply ``Linear(LayerNorm(x))`` to the UN-normalised ``x``: the weight
+    with the LayerNorm gain multiplied into its columns, its row sums, and the bias W beta + b."""
+
+    __slots__ = ("weight", "colsum", "bias_f32", "eps")
+
+    def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None, gamma: torch.Tensor | None, beta: torch.Tensor | None, eps: float):
+        w32 = weight.detach().float()
+        wg = (w32 * gamma.detach().float()[None, :]) if gamma is not None else w32
+        self.weight = wg.to(weight.dtype).contiguous()
+        # sums of the ROUNDED weights: the mean term then cancels exactly against the accumulator
+        self.colsum = self.weight.float().sum(dim=1).contiguous()
+        b = torch.zeros(weight.shape[0], device=weight.device, dtype=torch.float32) if bias is None else bias.detach().float().clone()
+        if beta is not None:
+            b += w32 @ beta.detach().float()
+        self.bias_f32 = b.contiguous()
+        self.eps = float(eps)
+
+
+_MAX_STAT_PARTS = 64
+
+
+def gemm_fused(a, w, *, bias=None, bias_f32=None, residual=None, out=None, out2=None, n_split=0, geglu=False,
+               ln: tuple | None = None, want_stats=False):
+    """``a[M,K] @ w[N,K]^T`` through the general entry point.  ``ln = (RowStats of a, FoldedLayerNorm)``
+    folds a LayerNorm over ``a``'s rows into the product (``w`` is then ignored in favour of the
+    folded weight); ``want_stats`` returns the RowStats of the fp16 output as a second value."""
+    _f16_cuda(a, "a")
+    M, K = a.shape
+    fold = None
+    if ln is not None:
+        stats_in, fold = ln
+        w, bias, bias_f32 = fold.weight, None, fold.bias_f32
+        _req(stats_in.buf.shape[0] == M and stats_in.buf.is_contiguous(), "gemm_fused: row statistics do not match a")
+    _f16_cuda(w, "w")
+    N = w.shape[0]
+    _req(a.dim() == 2 and w.shape[1] == K and a.stride(1) == 1 and w.stride(1) == 1, "gemm_fused: bad operands")
+    n_out = N // 2 if geglu else (n_split if n_split else N)
+    if out is None:
+        out = torch.empty((M, n_out), device=a.device, dtype=torch.float16)
+    _req(out.shape == (M, n_out) and out.stride(1) == 1, "gemm_fused: bad output")
+    if n_split:
+        if out2 is None:
+            out2 = torch.empty((M, N - n_split), device=a.device, dtype=torch.float16)
+        _req(out2.shape == (M, N - n_split) and out2.stride(1) == 1, "gemm_fused: bad second output")
+    if residual is not None:
+        _req(residual.shape == (M, N) and residual.stride(1) == 1, "gemm_fused: bad residual")
+    args = _lib.GemmFusedArgs()
+    args.A, args.lda, args.B, args.ldb = _p(a), a.stride(0), _p(w), w.stride(0)
+    args.bias, args.bias_f32 = _p(bias), _p(bias_f32)
+    args.residual, args.ldr = _p(residual), 0 if residual is None else residual.stride(0)
+    args.C, args.ldc = _p(out), out.stride(0)
+    args.C2, args.ldc2, args.n_split = (_p(out2), out2.stride(0), n_split) if n_split else (None, 0, 0)
+    args.geglu = int(geglu)
+    if ln is not None:
+        args.ln_partials, args.ln_parts = _p(stats_in.buf), stats_in.parts
+        args.ln_colsum, args.ln_eps = _p(fold.colsum), fold.eps
+    stats = None
+    if want_stats:
+        buf = torch.empty((M, min(_MAX_STAT_PARTS, max(1, N // 32)), 2), device=a.device, dtype=torch.float32)
+        args.row_stats, args.row_stats_capacity = _p(buf), buf.numel()
+    args.M, args.N, args.K = M, N, K
+    parts = C.c_int(0)
+    l = _lib.lib()
+    _lib.check(l.bxl_gemm_fused_f16(C.byref(args), C.byref(parts), _stream()), l)
+    if want_stats:
+        # the partials of row m live at buf.view(-1)[m * parts * 2 ...]: re-view with the real count
+        stats = RowStats(buf.view(-1)[: M * parts.value * 2].view(M, parts.value, 2), parts.value)
+    if n_split:
+        return (out, out2, stats) if want_stats else (out, out2)
+    return (out, stats) if want_stats else out
+
+
 def gemm_split_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """fp32 ``a[M,K] @ b[K,N]`` through the split-operand tensor-core product."""
     _req(a.is_cuda and a.dtype == torch.float32 and b.dtype == torch.float32, "gemm_split_f32: CUDA fp32 operands")

@@ -81,6 +81,7 @@ class BasedXLUnet(BaseModel):
                 "CUDA graphs (BasedXLPipeline(..., cuda_graph=True)) instead"
             )
         super().__init__(model, cfg)
+        self.prepack_weights()
         self.cuda_graph = False
         self._graphed = None        # displaced steps (single GPU: every step)
         self._graphed_sync = None   # synchronous warm-up steps of a patch-parallel run
@@ -97,6 +98,17 @@ class BasedXLUnet(BaseModel):
             if getattr(self, slot, None) is not None:
                 getattr(self, slot).release()
             setattr(self, slot, None)
+
+    @torch.no_grad()
+    def prepack_weights(self):
+        """Build the tap-major copies of the 3x3 convolution weights now rather than at each
+        layer's first call, so that no packing kernel is launched in the middle of a step.
+        (Weights loaded later are re-packed at the layer's next call.)"""
+        from .modules.conv2d import packed_weight
+
+        for m in self.model.modules():
+            if isinstance(m, nn.Conv2d) and tuple(m.kernel_size) == (3, 3) and m.weight.is_cuda and m.weight.dtype == torch.float16:
+                packed_weight(m)
 
     def patch_linear_layers(self, model: nn.Module):
         for _name, module in model.named_modules():

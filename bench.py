@@ -13,9 +13,10 @@ displaced steps, like a real image.  ``e2e`` is the same figure measured through
 final latent copied back out inside the timed region.
 
 ``--impl reference`` times the reference's CPU path instead: the same UNet graph
-evaluated by stock PyTorch fp32 operators on the host cores (the reference has no
-CPU implementation other than its PyTorch modules on CPU tensors), on a bounded
-sample per step, extrapolated to s/image by algorithmic FLOPs.
+evaluated by stock PyTorch fp32 operators on all host cores (the reference has no
+CPU implementation other than its PyTorch modules on CPU tensors).  A step of that
+arm is one full-size UNet forward on the CFG batch of 2 - the same configuration
+as the accelerated arm, no extrapolation over the problem size.
 
 Synthetic data throughout: N(0,1) latents and conditioning, seed-0 random
 weights of the SDXL architecture.
@@ -122,57 +123,94 @@ def synthetic_inputs(height, width, pin: bool):
 
 
 # --------------------------------------------------------------------------- GEMM kernel roofline
-def gemm_kernel_roofline(device, n_strips: int, height: int, width: int, peaks) -> dict:
-    """The dominant kernel (the tcgen05 GEMM: 64 % of the loop's FLOPs at 1024^2) over the UNet's
-    own linear-layer shapes.  For every shape the launches cycle through enough operand sets
-    (activations, weights, outputs) to exceed the 126 MB L2 several times over, so every
-    launch reads its operands from HBM as in the real loop (5 GB of weights per step); the
-    chain is timed with CUDA events on the launching stream and divided by the number of
-    launches.  ``achieved`` = sum of algorithmic FLOPs (2*M*N*K) / sum of launch durations."""
-    from basedxl_b200 import ops
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "gemm_linear_traffic.txt")
 
+
+def measured_traffic():
+    """DRAM bytes per launch of the GEMM kernel from the committed profiler capture (a text
+    summary under profiles/: ``key: value`` lines).  None if the summary is absent."""
+    if not os.path.exists(TRAFFIC_FILE):
+        return None
+    kv = {}
+    with open(TRAFFIC_FILE) as f:
+        for ln in f:
+            if ":" in ln and not ln.startswith("#"):
+                k, v = ln.split(":", 1)
+                kv[k.strip()] = v.strip()
+    try:
+        return {"bytes_per_launch": float(kv["dram_bytes_read"]) + float(kv["dram_bytes_write"]), "case": kv["case"],
+                "algorithmic_bytes": float(kv["algorithmic_bytes"]), "capture": "profiles/gemm_linear_traffic.txt"}
+    except (KeyError, ValueError):
+        return None
+
+
+def linear_shapes(n_strips: int, height: int, width: int, batch: int):
+    """(tokens, K, N, launches per UNet forward) of the linear layers one rank runs."""
     hw = (height // 8) * (width // 8) // n_strips
-    # (tokens, K, N, launches per UNet forward) of the per-rank (b = 1 at N > 1, b = 2 at N = 1) linears
-    b = 2 if n_strips == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1 else 1
-    shapes = [
+    b = batch
+    return [
         (b * hw // 4, 640, 640, 40), (b * hw // 4, 640, 1920, 10), (b * hw // 4, 640, 5120, 10), (b * hw // 4, 2560, 640, 10),
         (b * hw // 16, 1280, 1280, 192), (b * hw // 16, 1280, 3840, 60), (b * hw // 16, 1280, 10240, 60), (b * hw // 16, 5120, 1280, 60),
     ]
+
+
+def gemm_kernel_roofline(device, n_strips: int, height: int, width: int, peaks) -> dict:
+    """The dominant kernel (the tcgen05 GEMM: 64 % of the loop's FLOPs at 1024^2) over the UNet's
+    own linear-layer shapes.  For every shape a chain of launches cycles through enough operand
+    sets (activations, weights, outputs) to exceed the 126 MB L2 several times over, so every
+    launch reads its operands from HBM as in the real loop (5 GB of weights per step).  The
+    chain is captured into a CUDA graph and REPLAYED, as the UNet step is, so the host's launch
+    cost is not in the figure; it is timed with CUDA events on the replaying stream and divided
+    by the number of launches.  ``achieved`` = sum of algorithmic FLOPs (2*M*N*K) / sum of launch
+    durations, weighted by launches per forward."""
+    from basedxl_b200 import _lib, ops
+
+    b = 2 if n_strips == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1 else 1
     stream = torch.cuda.current_stream()
     tot_flops = tot_ms = 0.0
     per_shape = []
-    for (M, K, N, count) in shapes:
-        set_bytes = 2 * (M * K + N * K + M * N)
-        n_sets = max(4, min(48, (512 << 20) // set_bytes + 1))  # >= 512 MB cycled through
-        a = [torch.randn(M, K, device=device).half() for _ in range(n_sets)]
-        w = [torch.randn(N, K, device=device).half() for _ in range(n_sets)]
-        out = [torch.empty(M, N, device=device, dtype=torch.float16) for _ in range(n_sets)]
-        for i in range(n_sets):
-            ops.gemm(a[i], w[i], out=out[i])
-        times = []
-        for _ in range(3):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
+    l = _lib.lib()
+    _lib.check(l.bxl_set_static_weights(1), l, kernels=0)  # as inside a UNet step: B operands are weights
+    try:
+        for (M, K, N, count) in linear_shapes(n_strips, height, width, b):
+            set_bytes = 2 * (M * K + N * K + M * N)
+            n_sets = max(4, min(48, (512 << 20) // set_bytes + 1))  # >= 512 MB cycled through
+            a = [torch.randn(M, K, device=device).half() for _ in range(n_sets)]
+            w = [torch.randn(N, K, device=device).half() for _ in range(n_sets)]
+            out = [torch.empty(M, N, device=device, dtype=torch.float16) for _ in range(n_sets)]
             for i in range(n_sets):
                 ops.gemm(a[i], w[i], out=out[i])
-            e1.record(stream)
-            e1.synchronize()
-            times.append(e0.elapsed_time(e1) / n_sets)
-        ms = statistics.median(times)
-        fl = 2.0 * M * N * K
-        per_shape.append({"M": M, "K": K, "N": N, "launches_per_forward": count, "us": round(ms * 1e3, 2), "tflops": round(fl / ms / 1e9, 1)})
-        tot_flops += fl * count
-        tot_ms += ms * count
-        del a, w, out
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for i in range(n_sets):
+                    ops.gemm(a[i], w[i], out=out[i])
+            graph.replay()
+            times = []
+            for _ in range(5):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                graph.replay()
+                e1.record(stream)
+                e1.synchronize()
+                times.append(e0.elapsed_time(e1) / n_sets)
+            ms = statistics.median(times)
+            fl = 2.0 * M * N * K
+            per_shape.append({"M": M, "K": K, "N": N, "launches_per_forward": count, "us": round(ms * 1e3, 2), "tflops": round(fl / ms / 1e9, 1)})
+            tot_flops += fl * count
+            tot_ms += ms * count
+            graph.reset()
+            del graph, a, w, out
+    finally:
+        _lib.check(l.bxl_set_static_weights(0), l, kernels=0)
     achieved = tot_flops / tot_ms / 1e9
     return {
         "bound": "tensor", "kernel": "gemm_conv_kernel (linear layers)", "achieved": round(achieved, 1),
         "peak": peaks["tflops_burst"], "peak_kind": f"{peaks['source']} burst (kernel timed alone)", "unit": "TFLOP/s",
         "frac": round(achieved / peaks["tflops_burst"], 4),
+        "timing": "device: chains of launches replayed from a CUDA graph, CUDA events on the replaying stream",
         "l2": "operand sets cycled, > 512 MB per shape (larger than L2)",
-        # dram__bytes_read + dram__bytes_write of one launch of this kernel under ncu (profiles/gemm_8192x2560x5120.md):
-        # 81.9 + 58.1 MB for M=8192 K=2560 N=5120, whose algorithmic bytes are 68 MB read + 84 MB written
-        "traffic": {"bytes_per_launch": 140.0e6, "case": "M=8192 K=2560 N=5120", "algorithmic_bytes": 151.9e6},
+        "traffic": measured_traffic(),
         "per_shape": per_shape,
     }
 
@@ -207,39 +245,43 @@ def cpu_forward_seconds(model, latent_hw: int, batch: int = 2) -> float:
 
 
 def run_reference_arm(args):
-    """The reference's CPU path: stock PyTorch fp32 modules on the host cores."""
+    """The reference's CPU path: stock PyTorch fp32 modules on all host cores, one full-size
+    UNet forward (CFG batch 2) per step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from basedxl_b200.flops import unet_flops
-    from basedxl_b200.sdxl_unet import sdxl_config
-
-    cores = torch.get_num_threads()
+    # a launcher for several ranks pins OMP_NUM_THREADS=1; this arm is one process on the whole host
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
     model = cpu_unet()
-    sample_hw = 32  # latent 32 x 32 (a 256^2 image) per step: bounded sample of the 128 x 128 workload
-    full_hw = args.height // 8
-    ratio = unet_flops(sdxl_config(), full_hw, full_hw, 2) / unet_flops(sdxl_config(), sample_hw, sample_hw, 2)
-    for _ in range(args.warmup):
-        cpu_forward_seconds(model, sample_hw)
+    hw = args.height // 8
+    for _ in range(args.warmup_reference):
+        cpu_forward_seconds(model, hw)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        cpu_forward_seconds(model, sample_hw)
+        cpu_forward_seconds(model, hw)
     per_step = (time.perf_counter() - t0) / args.steps
-    value = per_step * ratio * IMAGE_STEPS
-    sample = (f"per step: one UNet forward, CFG batch 2, {sample_hw}x{sample_hw} latent, fp32, stock PyTorch CPU operators; "
-              f"extrapolated to the {full_hw}x{full_hw} latent by algorithmic FLOPs (x{ratio:.1f}) and to {IMAGE_STEPS} steps")
+    value = per_step * IMAGE_STEPS
+    sample = (f"per step: one UNet forward, CFG batch 2, {hw}x{hw} latent (the full-size workload), fp32, stock PyTorch CPU "
+              f"operators on {torch.get_num_threads()} threads; {args.steps} steps timed, s/image = {IMAGE_STEPS} x mean step")
     line = {
         "impl": "reference", "metric": metric_name(args.height), "value": round(value, 2), "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": round(per_step * ratio * 1e3, 1), "higher_is_better": False, "scaling": "strong",
+        "warmup": args.warmup, "ms_per_step": round(per_step * 1e3, 1), "higher_is_better": False, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"SDXL {args.height}x{args.width} UNet loop, 50 Euler steps, CFG batch 2 (CPU path of the reference: PyTorch modules on host cores)"},
-        "cpu_baseline": {"value": round(value, 2), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "config": {"workload": workload_name(args), "arm": "CPU path of the reference: PyTorch modules on host cores",
+                   "warmup_steps_run": args.warmup_reference},
+        "cpu_baseline": {"value": round(value, 2), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": round(value, 2), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
 # --------------------------------------------------------------------------- main arm
+def workload_name(args) -> str:
+    return (f"SDXL {args.height}x{args.width} UNet loop: latent 1x4x{args.height // 8}x{args.width // 8}, CFG batch 2, guidance 5.0, "
+            f"50 Euler steps, 5 synchronous steps then displaced")
+
+
 def run_b200_arm(args):
     from basedxl_b200 import _lib
     from basedxl_b200.flops import unet_flops
@@ -274,32 +316,43 @@ def run_b200_arm(args):
         return float(t.item())
 
     stream = torch.cuda.current_stream()
+    steps_total = max(IMAGE_STEPS, args.steps)
+
+    def timed_image(lat, ehs, added):
+        """Steps 0..K-1 of a fresh image on device-resident inputs: (max-over-ranks ms, launches, latents)."""
+        pipe.unet.reset()
+        launches0 = _lib.launches
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        out = pipe.denoise(lat, ehs, added, steps_total, 5.0, first_step=0, last_step=args.steps)
+        e1.record(stream)
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1)), _lib.launches - launches0, out
+
     # ---- device-resident loop -------------------------------------------------
     lat, ehs, added = pipe.prepare_inputs(**host)
     pipe.unet.reset()
-    # Untimed warm-up steps.  A patch-parallel run captures its second CUDA graph (the displaced
-    # step) at step warmup_steps + 1 of an image: the warm-up is extended to include that step, so
-    # that no graph capture falls into the timed region.
-    warm_steps = max(args.warmup, 1)
-    if not args.no_graph and cfg.n_device_per_batch > 1:
-        warm_steps = max(warm_steps, cfg.warmup_steps + 2)
-    pipe.denoise(lat, ehs, added, IMAGE_STEPS, 5.0, first_step=0, last_step=warm_steps)
+    # Untimed warm-up.  One GPU: W steps (the first one captures the step graph).  Several GPUs: a
+    # complete image of at least K steps, so that everything an image does once per process - the
+    # eager first step, the capture of the synchronous-step and displaced-step graphs, NCCL's
+    # channel set-up on their first replay, the allocator's growth - lies outside the timed region.
+    warm_steps = max(args.warmup, 3)
+    if world > 1:
+        warm_steps = max(warm_steps, args.steps, cfg.warmup_steps + 2)
+    pipe.denoise(lat, ehs, added, steps_total, 5.0, first_step=0, last_step=min(warm_steps, steps_total))
     barrier()
-    pipe.unet.reset()
     sampler = ClockSampler(dev.index if dev.index is not None else 0)
     sampler.start()
-    launches0 = _lib.launches
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    out = pipe.denoise(lat, ehs, added, max(IMAGE_STEPS, args.steps), 5.0, first_step=0, last_step=args.steps)
-    e1.record(stream)
-    barrier()
-    ms_total = max_over_ranks(e0.elapsed_time(e1))
-    launches = _lib.launches - launches0
+    ms_total, launches, out = timed_image(lat, ehs, added)
     clocks = sampler.stop()
+    comm0 = pipe.unet.comm_manager.bytes_sent if pipe.unet.comm_manager is not None else 0
+    ms_second, _, out2 = timed_image(lat, ehs, added)
+    comm_bytes_image = (pipe.unet.comm_manager.bytes_sent - comm0) if pipe.unet.comm_manager is not None else 0
     _lib.device_status()
     assert torch.isfinite(out).all(), "non-finite latents"
+    # the same image twice: the loop (graph replay included) must be deterministic
+    repeat_err = float((out2.float() - out.float()).norm() / out.float().norm())
     ms_per_step = ms_total / args.steps
     value = ms_per_step * IMAGE_STEPS / 1e3
 
@@ -308,7 +361,8 @@ def run_b200_arm(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     res = pipe(host["prompt_embeds"], host["pooled_prompt_embeds"], host["negative_prompt_embeds"],
-               host["negative_pooled_prompt_embeds"], num_inference_steps=args.steps, guidance_scale=5.0, latents=host["latents"])
+               host["negative_pooled_prompt_embeds"], num_inference_steps=steps_total, guidance_scale=5.0, latents=host["latents"],
+               last_step=args.steps)
     final = res.latents.to("cpu", non_blocking=False)
     e1.record(stream)
     barrier()
@@ -316,6 +370,8 @@ def run_b200_arm(args):
     h2d = sum(v.numel() * v.element_size() for v in host.values())
     d2h = final.numel() * final.element_size()
     e2e_value = e2e_ms / args.steps * IMAGE_STEPS / 1e3
+    # the public call ran the same steps on the same inputs as the device-resident loop
+    e2e_err = float((final.float() - out.float().cpu()).norm() / out.float().norm().cpu())
 
     # ---- roofline of the dominant kernel ----------------------------------------------
     n_strips = cfg.n_device_per_batch
@@ -328,6 +384,7 @@ def run_b200_arm(args):
     # ---- CPU baseline on the host cores (rank 0, N = 1 only) --------------------------------
     cpu = None
     if world == 1 and not args.skip_cpu:
+        torch.set_num_threads(os.cpu_count() or 1)
         model = cpu_unet(pipe.unet.model.state_dict())
         secs = cpu_forward_seconds(model, args.height // 8)
         cpu = {"value": round(secs * IMAGE_STEPS, 1), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
@@ -340,13 +397,19 @@ def run_b200_arm(args):
             "metric": metric_name(args.height), "value": round(value, 4), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms_per_step, 3), "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
-            "config": {"workload": f"SDXL {args.height}x{args.width} UNet loop: latent 1x4x{args.height // 8}x{args.width // 8}, CFG batch 2, guidance 5.0, 50 Euler steps, 5 synchronous steps then displaced",
+            "config": {"workload": workload_name(args),
                        "parallelism": par, "l2": "activations and weights per step (5 GB of fp16 weights) exceed L2; no explicit flush in the loop",
                        "warmup_steps_run": warm_steps},
             "clocks": clocks, "gpu_launches": launches, "cuda_graph": bool(pipe.unet.cuda_graph),
-            "e2e": {"value": round(e2e_value, 4), "unit": UNIT, "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps},
+            "e2e": {"value": round(e2e_value, 4), "unit": UNIT, "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps,
+                    "rel_l2_vs_device_resident_run": e2e_err},
+            "second_image": {"ms_per_step": round(ms_second / args.steps, 3), "rel_l2_vs_first": repeat_err},
             "roofline": roof,
         }
+        if world > 1:
+            # own contribution handed to the stale-exchange gathers (displaced steps) per image and rank
+            line["comm"] = {"exchange_bytes_per_rank_per_image": comm_bytes_image, "steps": args.steps,
+                            "note": "asynchronous gathers run on the communication stream and are joined one step later"}
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
@@ -354,22 +417,31 @@ def run_b200_arm(args):
 
 
 def shutdown(pipe, world):
-    """Release captured graphs before the process group goes away; a watchdog ends
-    the process if tear-down stalls, so that a finished run never blocks its launcher."""
+    """Release the captured graphs, then the process group, then return so that the interpreter
+    exits normally.  A watchdog turns a stalled tear-down into a loud non-zero exit instead of
+    a hang."""
     sys.stdout.flush()
-    threading.Timer(30.0, lambda: os._exit(0)).start()
+
+    def stalled():
+        sys.stderr.write("bench.py: tear-down did not finish within 60 s (graph release / process-group destruction stalled)\n")
+        sys.stderr.flush()
+        os._exit(3)
+
+    watchdog = threading.Timer(60.0, stalled)
+    watchdog.daemon = True
+    watchdog.start()
     pipe.unet.release_graph()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
-    os._exit(0)
+    watchdog.cancel()
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=IMAGE_STEPS)
+    ap.add_argument("--steps", type=int, default=None, help="timed steps (default: 50; reference arm: 10 full-size CPU forwards)")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--height", type=int, default=1024)
@@ -379,9 +451,14 @@ def main():
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    args.warmup_reference = args.warmup
     if args.impl == "reference":
+        if args.steps is None:
+            args.steps = 10  # default run: ten full-size CPU forwards, a couple of minutes
         run_reference_arm(args)
     else:
+        if args.steps is None:
+            args.steps = IMAGE_STEPS
         run_b200_arm(args)
 
 

@@ -94,6 +94,37 @@ int bxl_gemm_dual_f16(const void* A, long long lda, const void* B, long long ldb
 int bxl_gemm_geglu_f16(const void* A, long long lda, const void* B, long long ldb, const void* bias, void* C,
                        long long ldc, int M, int N, int K, void* stream);
 
+/* General form of the three entry points above (B as [N,K]), with two additions that remove the
+ * LayerNorm kernels of the transformer blocks from the step:
+ *   - row statistics out: with `row_stats` set, every CTA also writes, per output row, the sum and
+ *     the sum of squares of the fp16 values it stored for the column slice it owns:
+ *     row_stats[m][part][2] fp32, `*row_stats_parts` partials per row (the count follows from
+ *     the tiling chosen for the problem and is at most N/32; row_stats_capacity = floats available);
+ *   - LayerNorm folded in: with `ln_partials` set (such partials of the rows of A, `ln_parts` per
+ *     row), A is taken as the UN-normalised input of a LayerNorm over K, B as the weight with the
+ *     LayerNorm gain multiplied into its columns, `ln_colsum[n]` = sum_k B[n,k] (fp32), and the
+ *     bias (`bias_f32`, fp32) as W * beta + b: the epilogue forms
+ *     rstd_m * (acc[m,n] - mean_m * ln_colsum[n]) + bias[n], which equals Linear(LayerNorm(A)).
+ * Everything else as in bxl_gemm_f16 / bxl_gemm_dual_f16 (C2, ldc2, n_split) / bxl_gemm_geglu_f16
+ * (geglu = 1).  Unused pointers are NULL, unused integers 0.
+ * Replaces: the LayerNorm -> Linear pairs of the host UNet's transformer blocks (norm1 -> to_q/to_kv,
+ * norm2 -> to_q, norm3 -> feed-forward projection) around the attention wrappers
+ * (basedxl/modules/attn.py:123,127). */
+typedef struct bxl_gemm_fused_args {
+  const void* A; long long lda;
+  const void* B; long long ldb;
+  const void* bias;
+  const float* bias_f32;
+  const void* residual; long long ldr;
+  void* C; long long ldc;
+  void* C2; long long ldc2; int n_split;
+  int geglu;
+  const float* ln_partials; int ln_parts; const float* ln_colsum; float ln_eps;
+  float* row_stats; long long row_stats_capacity;
+  int M, N, K;
+} bxl_gemm_fused_args;
+int bxl_gemm_fused_f16(const bxl_gemm_fused_args* args, int* row_stats_parts, void* stream);
+
 /* Split-operand product of fp32 matrices: A[M,K] and B[K,N] (row-major fp32) are
  * each split into fp16 high and low parts and C = Ah*Bh + Ah*Bl + Al*Bh is
  * accumulated in one fp32 tensor-memory accumulator; C is fp32 [M,N].

@@ -15,7 +15,10 @@ counters.
 For each configuration (world size, CFG on/off) every rank runs the same
 seeded 8-step Euler loop (5 synchronous steps, then 3 displaced ones); rank 0's
 per-step UNet outputs and final latents are stored in
-``tests/golden/unet_pp_loop.npz`` together with the inputs.  ``comm_checkpoint``
+``tests/golden/unet_pp_loop.npz`` together with the inputs.  The 8-rank
+configuration (CFG halves x 4 strips) is the layout of an 8-GPU run; one
+configuration is also run for all 50 steps of the schedule (final latents and
+the UNet outputs of a few steps are kept).  ``comm_checkpoint``
 is set to 10 so that the miniature's 37 exchanged tensors are gathered in
 several chunks plus a tail, as the full network's 155 are with the default 60.
 """
@@ -39,7 +42,10 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 STEPS, TOTAL_STEPS, GUIDANCE, LATENT, CKPT = 8, 50, 5.0, 32, 10
-CONFIGS = [("ws2_nocfg", 2, False), ("ws4_cfg", 4, True), ("ws4_nocfg", 4, False)]
+# (tag, world size, CFG split, steps run)
+CONFIGS = [("ws2_nocfg", 2, False, STEPS), ("ws4_cfg", 4, True, STEPS), ("ws4_nocfg", 4, False, STEPS),
+           ("ws8_cfg", 8, True, STEPS), ("ws4_cfg_50", 4, True, TOTAL_STEPS)]
+KEPT_STEPS_LONG = [0, 4, 5, 6, 24, 49]  # UNet outputs kept from the 50-step run
 
 
 def loop_inputs(cfg):
@@ -108,7 +114,7 @@ def load_reference(root):
     return utils, unet
 
 
-def worker(rank, world, use_cfg, ref_root, port, ret):
+def worker(rank, world, use_cfg, steps, ref_root, port, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     torch.set_num_threads(2)
@@ -140,7 +146,7 @@ def worker(rank, world, use_cfg, ref_root, port, ret):
         cm.create_buffer()
         wrapped.set_counter(0)
         call = lambda x, t, e, a: wrapped(x, t, e, added_cond_kwargs=a)[0]
-        lat, outs = euler_loop(call, inp, EulerDiscreteScheduler())
+        lat, outs = euler_loop(call, inp, EulerDiscreteScheduler(), steps=steps)
         cm.clear()
     if rank == 0:
         ret["latents"] = lat.numpy()
@@ -160,11 +166,15 @@ def main():
     args = ap.parse_args()
     blob = {}
     mgr = mp.Manager()
-    for n, (tag, world, use_cfg) in enumerate(CONFIGS):
+    for n, (tag, world, use_cfg, steps) in enumerate(CONFIGS):
         ret = mgr.dict()
-        mp.spawn(worker, args=(world, use_cfg, args.reference, 29540 + n, ret), nprocs=world, join=True)
+        mp.spawn(worker, args=(world, use_cfg, steps, args.reference, 29540 + n, ret), nprocs=world, join=True)
         blob[f"{tag}_latents"] = ret["latents"]
-        blob[f"{tag}_outs"] = ret["outs"].astype(np.float32)
+        outs = ret["outs"].astype(np.float32)
+        if steps > STEPS:
+            outs = outs[KEPT_STEPS_LONG]
+            blob[f"{tag}_kept_steps"] = np.array(KEPT_STEPS_LONG)
+        blob[f"{tag}_outs"] = outs
         blob[f"{tag}_n_registered"] = np.int64(ret["n_registered"])
         blob[f"{tag}_numel"] = np.int64(ret["numel"])
         if n == 0:

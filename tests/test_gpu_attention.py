@@ -109,13 +109,13 @@ def test_benchmark_shape_self_attention():
     kv_prev = h16(kv + 0.01 * torch.randn(2, L, 2 * C, generator=gen))
     q = h16(torch.randn(2, L, C, generator=gen))
     for n in (2, 4, 8):
-        i = n - 1
         ls = L // n
-        slots = [(kv if j == i else kv_prev)[:, j * ls : (j + 1) * ls] for j in range(n)]
-        ref = po._sdpa_heads(q[:, i * ls : (i + 1) * ls], torch.cat(slots, dim=1), heads)
-        y = ops.attention(q[:, i * ls : (i + 1) * ls].half().to(dev), [s.half().to(dev).contiguous() for s in slots], heads)
-        _lib.device_status()
-        assert_close(y, ref, what=f"self-attention n={n}")
+        for i in sorted({0, n // 2, n - 1}):  # first, middle and last strip: the fresh slot in every position
+            slots = [(kv if j == i else kv_prev)[:, j * ls : (j + 1) * ls] for j in range(n)]
+            ref = po._sdpa_heads(q[:, i * ls : (i + 1) * ls], torch.cat(slots, dim=1), heads)
+            y = ops.attention(q[:, i * ls : (i + 1) * ls].half().to(dev), [s.half().to(dev).contiguous() for s in slots], heads)
+            _lib.device_status()
+            assert_close(y, ref, what=f"self-attention strip {i} of n={n}")
 
 
 @pytest.mark.parametrize("split", [1, 2, 4])
@@ -140,3 +140,21 @@ def test_attention_kv_split_over_a_cluster(B, heads, Lq, Lslot, nslots, split):
     finally:
         _lib.check(l.bxl_debug_force_attn_split(0), l, kernels=0)
     assert_close(y, ref, tol=3e-3, what=f"attention split={split}")
+
+
+def test_self_attention_at_16384_tokens():
+    """The 2048 x 2048 image's highest-resolution attention (L = 16384 keys): one head, the
+    last of 4 strips (4096 queries), stale K/V in the other three slots."""
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    gen = torch.Generator().manual_seed(5)
+    C, heads, L, n = 64, 1, 16384, 4
+    kv = h16(torch.randn(1, L, 2 * C, generator=gen))
+    kv_prev = h16(kv + 0.01 * torch.randn(1, L, 2 * C, generator=gen))
+    q = h16(torch.randn(1, L, C, generator=gen))
+    ls, i = L // n, n - 1
+    slots = [(kv if j == i else kv_prev)[:, j * ls : (j + 1) * ls] for j in range(n)]
+    ref = po._sdpa_heads(q[:, i * ls : (i + 1) * ls], torch.cat(slots, dim=1), heads)
+    y = ops.attention(q[:, i * ls : (i + 1) * ls].half().to(dev), [s.half().to(dev).contiguous() for s in slots], heads)
+    _lib.device_status()
+    assert_close(y, ref, what="self-attention L=16384")

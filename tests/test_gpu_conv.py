@@ -74,12 +74,12 @@ def test_conv_benchmark_shape():
     for n in (2, 4, 8):
         xs, xps = torch.chunk(x, n, 2), torch.chunk(xp, n, 2)
         stale = [po.conv2d_boundary(t, 1) for t in xps]
-        i = n // 2
-        ref = po.conv2d_pp(xs[i], w, b, 1, 1, stale, i, n)
-        top, bot = _halo_rows(ops, dev, stale, i, n)
-        y = _conv(ops, dev, xs[i], w, b, 1, top, bot)
-        _lib.device_status()
-        assert_close(y, ref, what=f"conv strip n={n}")
+        for i in sorted({0, n // 2, n - 1}):  # top-edge, interior and bottom-edge strips
+            ref = po.conv2d_pp(xs[i], w, b, 1, 1, stale, i, n)
+            top, bot = _halo_rows(ops, dev, stale, i, n)
+            y = _conv(ops, dev, xs[i], w, b, 1, top, bot)
+            _lib.device_status()
+            assert_close(y, ref, what=f"conv strip {i} of n={n}")
 
 
 def test_conv_fused_epilogue():

@@ -71,7 +71,7 @@ def test_gemm_reference_unit_test_tolerance():
     assert torch.allclose(y.cpu(), expected, rtol=1e-3, atol=0.35)
 
 
-@pytest.mark.parametrize("M,K,N", [(8192, 640, 640), (2048, 1280, 1280), (16384, 320, 320)])
+@pytest.mark.parametrize("M,K,N", [(8192, 640, 640), (8192, 640, 5120), (2048, 1280, 1280), (2048, 1280, 10240), (16384, 320, 320)])
 def test_error_vs_fp64_no_worse_than_reference_kernel(M, K, N):
     """Method of the reference's error study: fp64 product as truth."""
     dev = cuda_or_skip()

@@ -54,7 +54,7 @@ def test_groupnorm_golden(golden_dir, n):
 
 
 @pytest.mark.parametrize("C,H,W", [(1280, 32, 32), (320, 128, 128), (960, 64, 64), (2560, 32, 32), (1920, 8, 32)])
-@pytest.mark.parametrize("n", [1, 2, 8])
+@pytest.mark.parametrize("n", [1, 2, 4, 8])
 def test_groupnorm_config_shapes(C, H, W, n):
     """32 groups on SDXL shapes (2 x 1280 x 32 x 32 is the benchmark configuration),
     split n ways along H, stale = current + N(0, 0.01)."""
@@ -68,13 +68,13 @@ def test_groupnorm_config_shapes(C, H, W, n):
     gamma, beta = torch.randn(C, generator=gen), torch.randn(C, generator=gen)
     xs, xps = torch.chunk(h16(x), n, 2), torch.chunk(h16(xp), n, 2)
     stale = [po.groupnorm_moments(t, 32) for t in xps]
-    i = n // 2
     mode = "stale" if n > 1 else "local"
-    ref = po.groupnorm_pp(xs[i], 32, 1e-5, h16(gamma), h16(beta), stale if n > 1 else None, i, mode)
-    y, _ = _run(ops, dev, xs[i], 32, 1e-5, gamma, beta, stale if n > 1 else None, i, mode)
-    assert_close(y, ref, what=f"gn {C}x{H}x{W} n={n}")
-    y, _ = _run(ops, dev, xs[i], 32, 1e-5, gamma, beta, stale if n > 1 else None, i, mode, silu=True)
-    assert_close(y, torch.nn.functional.silu(ref), what="gn+silu")
+    for i in sorted({0, n // 2, n - 1}):  # first, middle and last strip
+        ref = po.groupnorm_pp(xs[i], 32, 1e-5, h16(gamma), h16(beta), stale if n > 1 else None, i, mode)
+        y, _ = _run(ops, dev, xs[i], 32, 1e-5, gamma, beta, stale if n > 1 else None, i, mode)
+        assert_close(y, ref, what=f"gn {C}x{H}x{W} n={n} strip {i}")
+        y, _ = _run(ops, dev, xs[i], 32, 1e-5, gamma, beta, stale if n > 1 else None, i, mode, silu=True)
+        assert_close(y, torch.nn.functional.silu(ref), what="gn+silu")
     _lib.device_status()
 
 

@@ -23,7 +23,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, use_cfg, graph, port, ret):
+def _worker(rank, world, use_cfg, graph, steps, port, ret):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(world), RANK=str(rank), LOCAL_RANK=str(rank))
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -62,7 +62,7 @@ def _worker(rank, world, use_cfg, graph, port, ret):
     for image in range(2):
         outs.clear()
         pipe.unet.reset()
-        final = pipe.denoise(T("in_latents").float(), T("in_ehs").half(), added, TOTAL_STEPS, GUIDANCE, first_step=0, last_step=STEPS)
+        final = pipe.denoise(T("in_latents").float(), T("in_ehs").half(), added, TOTAL_STEPS, GUIDANCE, first_step=0, last_step=steps)
     pipe.unet.comm_manager.clear()
     torch.cuda.synchronize()
     _lib.device_status()
@@ -73,7 +73,9 @@ def _worker(rank, world, use_cfg, graph, port, ret):
     dist.barrier()
     import threading
 
-    threading.Timer(20.0, lambda: os._exit(0)).start()  # backstop: never let tear-down stall the test
+    t = threading.Timer(60.0, lambda: os._exit(3))  # a stalled tear-down fails the test instead of hanging it
+    t.daemon = True
+    t.start()
     dist.destroy_process_group()
 
 
@@ -81,16 +83,25 @@ def _rel(a, b):
     return float(np.linalg.norm(a.astype(np.float64) - b) / np.linalg.norm(b.astype(np.float64)))
 
 
+# (tag, world size, CFG split, steps): 8 ranks = CFG halves x 4 strips, the layout of an 8-GPU run;
+# the last case runs all 50 steps of the schedule
+CASES = [("ws2_nocfg", 2, False, STEPS), ("ws4_cfg", 4, True, STEPS), ("ws4_nocfg", 4, False, STEPS), ("ws8_cfg", 8, True, STEPS),
+         ("ws4_cfg_50", 4, True, TOTAL_STEPS)]
+
+
 @pytest.mark.parametrize("graph", [False, True], ids=["eager", "graph"])
-@pytest.mark.parametrize("tag,world,use_cfg", [("ws2_nocfg", 2, False), ("ws4_cfg", 4, True), ("ws4_nocfg", 4, False)])
-def test_loop_on_gpus_matches_reference_run(tag, world, use_cfg, graph):
+@pytest.mark.parametrize("tag,world,use_cfg,steps", CASES, ids=[c[0] for c in CASES])
+def test_loop_on_gpus_matches_reference_run(tag, world, use_cfg, steps, graph):
     if not torch.cuda.is_available() or torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     g = np.load(GOLDEN)
     ret = mp.Manager().dict()
-    mp.spawn(_worker, args=(world, use_cfg, graph, _free_port(), ret), nprocs=world, join=True)
-    per_step = [_rel(ret["outs"][i], g[f"{tag}_outs"][i]) for i in range(STEPS)]
+    mp.spawn(_worker, args=(world, use_cfg, graph, steps, _free_port(), ret), nprocs=world, join=True)
+    kept = list(range(steps)) if steps == STEPS else [int(k) for k in g[f"{tag}_kept_steps"]]
+    per_step = [_rel(ret["outs"][k], g[f"{tag}_outs"][i]) for i, k in enumerate(kept)]
     print(tag, "per-step rel-L2", [f"{e:.2e}" for e in per_step], "final", _rel(ret["final"], g[f"{tag}_latents"]))
-    # fp16 kernels against the reference's fp32 CPU run: per-step bar 2e-3, final latents 1e-2
-    assert max(per_step) <= 2e-3, per_step
+    # fp16 kernels against the reference's fp32 CPU run: per-step bar 2e-3 (the drift of the latents
+    # accumulates over a 50-step run, where the bar is the final latents'), final latents 1e-2
+    if steps == STEPS:
+        assert max(per_step) <= 2e-3, per_step
     assert _rel(ret["final"], g[f"{tag}_latents"]) <= 1e-2

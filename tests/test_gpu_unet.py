@@ -67,6 +67,14 @@ def test_sdxl_unet_forward_matches_oracle_at_reduced_resolution():
     _compare(sdxl_config(), 32, 2e-3, "SDXL UNet forward, 32x32 latent")
 
 
+def test_sdxl_unet_forward_matches_oracle_at_full_resolution():
+    """The first benchmark configuration at its real size: CFG batch of 2, 128 x 128 latent,
+    timestep 999 (one fp32 CPU forward of 13.5 TFLOP: seconds on a multi-core host)."""
+    from basedxl_b200.sdxl_unet import sdxl_config
+
+    _compare(sdxl_config(), 128, 2e-3, "SDXL UNet forward, 128x128 latent")
+
+
 def test_tiny_unet_with_lowp_linear_swap_matches_oracle():
     """``fp16_acc_matmul=True``: every Linear replaced by BasedXLLowPLinear (weights kept as
     [K, N]), as the reference's patch_linear_layers does (basedxl/unet.py:81-87)."""
