@@ -51,6 +51,7 @@ SIGNATURES = {
     "bxl_groupnorm_stats_noalloc_max_bg": (_ll, []),
     "bxl_groupnorm_stats_noalloc_f16": (_i, [_vp, _ll, _i, _i, _i, _i, _vp, _vp]),
     "bxl_groupnorm_apply_f16": (_i, [_vp, _vp, _ll, _i, _i, _i, _i, _vp, C.POINTER(_vp), _i, _i, _i, _f, _vp, _vp, _i, _vp]),
+    "bxl_groupnorm_fused_f16": (_i, [_vp, _vp, _ll, _i, _i, _i, _i, _i, _vp, C.POINTER(_vp), _i, _i, _i, _f, _vp, _vp, _i, _vp, _vp]),
     "bxl_attn_fwd_f16": (_i, [_vp, _ll, _ll, C.POINTER(_vp), _i, _ll, _ll, _i, _vp, _ll, _ll, _i, _i, _i, _i, _f, _vp]),
     "bxl_upsample2x_f16": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
     "bxl_layernorm_f16": (_i, [_vp, _vp, _vp, _vp, _ll, _i, _f, _vp]),

@@ -211,6 +211,186 @@ __global__ void __launch_bounds__(512) groupnorm_apply_kernel(const __half* __re
   }
 }
 
+// ---- one-launch GroupNorm (local or stale moments) ------------------------------------
+// A thread-block cluster owns one (image, channel block); a channel block is the smallest run of
+// whole groups that is also a whole number of 16-byte vectors.  Each CTA of the cluster takes a
+// range of pixels: it reads its slab ONCE (keeping it in shared memory when it fits), reduces
+// the per-group sums, hands them to every CTA of the cluster through distributed shared
+// memory, and after one cluster barrier normalises its slab from shared memory.  The moments
+// the strip publishes are written by the cluster's first CTA, straight into the staging range
+// when the caller passes it; the strip's first and last pixel rows (what a following 3x3
+// convolution publishes to the neighbouring strips) can be written out on the way.
+constexpr int kGnfMaxGroupsPerBlock = 8;
+constexpr int kGnfMaxCluster = 8;
+
+struct GnFusedParams {
+  const __half* x;
+  __half* y;
+  long long img_stride;
+  int HW, C, G, B;
+  int cb;              // channels per block (multiple of 8 and of C / G)
+  int cs;              // CTAs per cluster (pixel ranges)
+  int keep;            // slab kept in shared memory between the two passes
+  float* fresh_out;    // [2][B][G] moments of this strip, or null
+  GnPeers peers;       // stale moments of every strip (mode 2)
+  int n_peers, own, mode;  // mode 0: local, 2: stale
+  float eps;
+  const __half* gamma;
+  const __half* beta;
+  int silu;
+  __half* halo_out;    // [2][B][W][C]: first and last pixel row of the strip's OUTPUT, or null
+  int W;
+};
+
+__global__ void __launch_bounds__(512) groupnorm_fused_kernel(const GnFusedParams p) {
+  pdl_launch_dependents();
+  extern __shared__ __align__(16) unsigned char gnf_smem[];
+  const int cb = p.cb, bv = cb / 8, cpg = p.C / p.G, gb = cb / cpg;
+  const int rows = blockDim.x / bv;                       // pixels per sweep
+  const uint32_t crank = p.cs > 1 ? cluster_ctarank() : 0u;
+  const int cblk = blockIdx.x / p.cs, img = blockIdx.y;
+  const int per = (p.HW + p.cs - 1) / p.cs;
+  const int p0 = min(p.HW, (int)crank * per), p1 = min(p.HW, p0 + per);
+  // shared-memory layout: exchange slots | per-group results | per-channel scale/shift | per-thread partials | slab
+  float* s_xch = reinterpret_cast<float*>(gnf_smem);                       // [cs][gb][2]
+  float* s_stat = s_xch + kGnfMaxCluster * kGnfMaxGroupsPerBlock * 2;      // [gb][2] mean, rstd; then stale terms [gb][4]
+  float* s_ab = s_stat + kGnfMaxGroupsPerBlock * 6;                        // [2][cb]
+  float* s_part = s_ab + 2 * cb;                                           // [rows][2][cb]
+  uint4* s_slab = reinterpret_cast<uint4*>(s_part + (size_t)rows * 2 * cb);  // [p1 - p0][bv] when kept
+  const int v = threadIdx.x % bv, r = threadIdx.x / bv;
+  const int g0 = cblk * gb;                               // first group of this block
+  pdl_wait();
+  // stale terms of this block's groups, read BEFORE any CTA publishes fresh moments into the
+  // same buffer: avg over the strips' stale moments and the own stale moments
+  if (p.mode == 2 && threadIdx.x < gb) {
+    const int g = g0 + threadIdx.x;
+    const long long i1 = (long long)img * p.G + g, i2 = ((long long)p.B + img) * p.G + g;
+    float a1 = 0.f, a2 = 0.f;
+    for (int j = 0; j < p.n_peers; ++j) a1 += p.peers.ptr[j][i1], a2 += p.peers.ptr[j][i2];
+    const float inv = 1.f / (float)p.n_peers;
+    float* t = s_stat + kGnfMaxGroupsPerBlock * 2 + threadIdx.x * 4;
+    t[0] = a1 * inv, t[1] = a2 * inv, t[2] = p.peers.ptr[p.own][i1], t[3] = p.peers.ptr[p.own][i2];
+  }
+  // ---- pass 1: read the slab, per-thread channel sums
+  float s1[8], s2[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s1[j] = s2[j] = 0.f;
+  const __half* xb = p.x + (long long)img * p.img_stride + (long long)cblk * cb + (long long)v * 8;
+  if (r < rows) {
+    int pix = p0 + r;
+    for (; pix + 3 * rows < p1; pix += 4 * rows) {
+      const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(xb + (long long)pix * p.C));
+      const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(xb + (long long)(pix + rows) * p.C));
+      const uint4 u2 = __ldg(reinterpret_cast<const uint4*>(xb + (long long)(pix + 2 * rows) * p.C));
+      const uint4 u3 = __ldg(reinterpret_cast<const uint4*>(xb + (long long)(pix + 3 * rows) * p.C));
+      if (p.keep) {
+        s_slab[(size_t)(pix - p0) * bv + v] = u0, s_slab[(size_t)(pix + rows - p0) * bv + v] = u1;
+        s_slab[(size_t)(pix + 2 * rows - p0) * bv + v] = u2, s_slab[(size_t)(pix + 3 * rows - p0) * bv + v] = u3;
+      }
+      accumulate8(u0, s1, s2), accumulate8(u1, s1, s2), accumulate8(u2, s1, s2), accumulate8(u3, s1, s2);
+    }
+    for (; pix < p1; pix += rows) {
+      const uint4 u = __ldg(reinterpret_cast<const uint4*>(xb + (long long)pix * p.C));
+      if (p.keep) s_slab[(size_t)(pix - p0) * bv + v] = u;
+      accumulate8(u, s1, s2);
+    }
+    float* d1 = s_part + ((size_t)r * 2) * cb + v * 8;
+    float* d2 = d1 + cb;
+    *reinterpret_cast<float4*>(d1) = make_float4(s1[0], s1[1], s1[2], s1[3]);
+    *reinterpret_cast<float4*>(d1 + 4) = make_float4(s1[4], s1[5], s1[6], s1[7]);
+    *reinterpret_cast<float4*>(d2) = make_float4(s2[0], s2[1], s2[2], s2[3]);
+    *reinterpret_cast<float4*>(d2 + 4) = make_float4(s2[4], s2[5], s2[6], s2[7]);
+  }
+  __syncthreads();
+  // ---- this CTA's per-group sums, in a fixed order, sent to every CTA of the cluster
+  {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    if (warp < warps) {
+      for (int i = warp; i < 2 * gb; i += warps) {
+        const int g = i >> 1, which = i & 1;
+        float acc = 0.f;
+        for (int e = lane; e < rows * cpg; e += 32) {
+          const int rr = e / cpg, c = e - rr * cpg;
+          acc += s_part[((size_t)rr * 2 + which) * cb + g * cpg + c];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane < p.cs) {
+          const uint32_t dst = smem_u32(&s_xch[((int)crank * kGnfMaxGroupsPerBlock + g) * 2 + which]);
+          if (p.cs > 1) st_cluster_f32(map_to_cta(dst, (uint32_t)lane), acc);
+          else s_xch[(g) * 2 + which] = acc;
+        }
+      }
+    }
+  }
+  if (p.cs > 1) cluster_sync_all();
+  else __syncthreads();
+  // ---- moments of the block's groups; combination with the stale moments; scale / shift
+  if (threadIdx.x < gb) {
+    const int g = threadIdx.x;
+    float a1 = 0.f, a2 = 0.f;
+    for (int j = 0; j < p.cs; ++j) a1 += s_xch[(j * kGnfMaxGroupsPerBlock + g) * 2], a2 += s_xch[(j * kGnfMaxGroupsPerBlock + g) * 2 + 1];
+    const float n = (float)((long long)cpg * p.HW);
+    const float f1 = a1 / n, f2 = a2 / n;
+    float m1 = f1, m2 = f2;
+    if (p.mode == 2) {
+      const float* t = s_stat + kGnfMaxGroupsPerBlock * 2 + g * 4;
+      m1 = t[0] + (f1 - t[2]);
+      m2 = t[1] + (f2 - t[3]);
+    }
+    float var = m2 - m1 * m1;
+    if (var < 0.f) var = f2 - f1 * f1;
+    var *= n / (n - 1.f);
+    s_stat[g * 2] = m1;
+    s_stat[g * 2 + 1] = rsqrtf(var + p.eps);
+    if (crank == 0 && p.fresh_out) {
+      p.fresh_out[(long long)img * p.G + g0 + g] = f1;
+      p.fresh_out[((long long)p.B + img) * p.G + g0 + g] = f2;
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < cb; c += blockDim.x) {
+    const int g = c / cpg, ch = cblk * cb + c;
+    const float ga = p.gamma ? __half2float(p.gamma[ch]) : 1.f;
+    const float be = p.beta ? __half2float(p.beta[ch]) : 0.f;
+    const float a = s_stat[g * 2 + 1] * ga;
+    s_ab[c] = a;
+    s_ab[cb + c] = be - s_stat[g * 2] * a;
+  }
+  __syncthreads();
+  // ---- pass 2: normalise (+ SiLU) and store
+  if (r >= rows) return;
+  float a[8], b[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) a[j] = s_ab[v * 8 + j], b[j] = s_ab[cb + v * 8 + j];
+  __half* yb = p.y + (long long)img * p.img_stride + (long long)cblk * cb + (long long)v * 8;
+  const int last_row0 = p.HW - p.W;
+  for (int pix = p0 + r; pix < p1; pix += rows) {
+    const uint4 u = p.keep ? s_slab[(size_t)(pix - p0) * bv + v] : *reinterpret_cast<const uint4*>(xb + (long long)pix * p.C);
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+    uint4 o;
+    __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __half22float2(h[j]);
+      float y0 = f.x * a[2 * j] + b[2 * j];
+      float y1 = f.y * a[2 * j + 1] + b[2 * j + 1];
+      if (p.silu) {
+        y0 = y0 * fmaf(0.5f, fast_tanh(0.5f * y0), 0.5f);
+        y1 = y1 * fmaf(0.5f, fast_tanh(0.5f * y1), 0.5f);
+      }
+      oh[j] = __floats2half2_rn(y0, y1);
+    }
+    *reinterpret_cast<uint4*>(yb + (long long)pix * p.C) = o;
+    if (p.halo_out) {
+      if (pix < p.W)
+        *reinterpret_cast<uint4*>(p.halo_out + ((long long)img * p.W + pix) * p.C + (long long)cblk * cb + v * 8) = o;
+      if (pix >= last_row0)
+        *reinterpret_cast<uint4*>(p.halo_out + (((long long)p.B + img) * p.W + (pix - last_row0)) * p.C + (long long)cblk * cb + v * 8) = o;
+    }
+  }
+}
+
 static int gn_threads(int C) {
   const int vecs = C / 8;
   int k = 512 / vecs;
@@ -285,6 +465,65 @@ extern "C" int bxl_groupnorm_apply_f16(const void* x, void* y, long long img_str
                        (cudaStream_t)stream, 1, static_cast<const __half*>(x), static_cast<__half*>(y), img_stride, HW, C, G, B,
                        fresh_moments, peers, mode == 0 ? 0 : n_peers, own, mode, eps, static_cast<const __half*>(gamma),
                        static_cast<const __half*>(beta), silu, parts);
+}
+
+// Channel block of the one-launch kernel: whole groups and whole 16-byte vectors.
+static int gnf_block_channels(int C, int G) {
+  const int cpg = C / G;
+  int cb = cpg;
+  while (cb % 8) cb += cpg;
+  return cb;
+}
+
+extern "C" int bxl_groupnorm_fused_f16(const void* x, void* y, long long img_stride, int B, int H, int W, int C, int G,
+                                       float* fresh_out, const float* const* peer_moments, int n_peers, int own, int mode,
+                                       float eps, const void* gamma, const void* beta, int silu, void* halo_out,
+                                       void* stream) {
+  const int HW = H * W;
+  if (int rc = gn_check("bxl_groupnorm_fused_f16", x, B, HW, C, G, img_stride)) return rc;
+  if (!y) return fail(kErrInvalidArg, "bxl_groupnorm_fused_f16: null output");
+  if (mode != 0 && mode != 2) return fail(kErrInvalidArg, "bxl_groupnorm_fused_f16: mode %d (0 = local, 2 = stale; the synchronous mode needs the two-launch form)", mode);
+  if (mode == 2 && (n_peers < 1 || n_peers > 8 || !peer_moments || own < 0 || own >= n_peers))
+    return fail(kErrInvalidArg, "bxl_groupnorm_fused_f16: bad peer table (n=%d own=%d)", n_peers, own);
+  const int cb = gnf_block_channels(C, G);
+  if (C % cb || cb / (C / G) > kGnfMaxGroupsPerBlock || cb > 512)
+    return fail(kErrUnsupported, "bxl_groupnorm_fused_f16: C=%d with %d groups does not split into channel blocks of whole groups and whole vectors", C, G);
+  if (halo_out && (reinterpret_cast<uintptr_t>(halo_out) & 15u)) return fail(kErrInvalidArg, "bxl_groupnorm_fused_f16: halo_out must be 16-byte aligned");
+  GnFusedParams p;
+  memset(&p, 0, sizeof(p));
+  for (int j = 0; j < 8; ++j) p.peers.ptr[j] = (mode == 2 && j < n_peers) ? peer_moments[j] : nullptr;
+  if (mode == 2)
+    for (int j = 0; j < n_peers; ++j)
+      if (!p.peers.ptr[j]) return fail(kErrInvalidArg, "bxl_groupnorm_fused_f16: peer %d null", j);
+  const int nblk = C / cb, bv = cb / 8;
+  // pixel ranges per cluster: enough CTAs to fill the machine, slabs small enough to keep on chip
+  int cs = 1;
+  while (cs < kGnfMaxCluster && ((long long)B * nblk * cs < 2ll * sm_count() && (long long)HW * cb * 2 / cs > 8192)) cs *= 2;
+  while (cs < kGnfMaxCluster && (long long)HW * cb * 2 / cs > 160 * 1024) cs *= 2;
+  const int per = (HW + cs - 1) / cs;
+  const long long slab = (long long)per * cb * 2;
+  int threads = 512;
+  auto fixed_smem = [&](int th) { return (size_t)(kGnfMaxCluster * kGnfMaxGroupsPerBlock * 2 + kGnfMaxGroupsPerBlock * 6 + 2 * cb) * 4 + (size_t)(th / bv) * 2 * cb * 4; };
+  if (slab + (long long)fixed_smem(512) > 200 * 1024 && slab + (long long)fixed_smem(256) <= 200 * 1024) threads = 256;
+  threads = (threads / bv) * bv;
+  const int keep = slab + (long long)fixed_smem(threads) <= 200 * 1024;
+  const size_t smem = fixed_smem(threads) + (keep ? (size_t)slab : 0) + 16;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (int rc = check_cuda(cudaFuncSetAttribute(groupnorm_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024),
+                            "cudaFuncSetAttribute(groupnorm_fused)"))
+      return rc;
+    configured[dev] = true;
+  }
+  p.x = static_cast<const __half*>(x), p.y = static_cast<__half*>(y), p.img_stride = img_stride;
+  p.HW = HW, p.C = C, p.G = G, p.B = B, p.cb = cb, p.cs = cs, p.keep = keep;
+  p.fresh_out = fresh_out, p.n_peers = mode == 2 ? n_peers : 0, p.own = own, p.mode = mode, p.eps = eps;
+  p.gamma = static_cast<const __half*>(gamma), p.beta = static_cast<const __half*>(beta), p.silu = silu;
+  p.halo_out = static_cast<__half*>(halo_out), p.W = W;
+  return launch_kernel("groupnorm_fused_kernel launch", groupnorm_fused_kernel, dim3(cs * nblk, B), dim3(threads), smem,
+                       (cudaStream_t)stream, cs, p);
 }
 
 // ---- statistics without caller-provided scratch ------------------------------------

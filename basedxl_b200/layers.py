@@ -14,7 +14,7 @@ import torch
 import torch.nn as nn
 
 from . import ops
-from .modules.attn import _finish, _lin, fuse_kv, qkv_project
+from .modules.attn import _finish, _folded, _lin, fuse_kv, qkv_project
 from .modules.base_module import as_nchw, as_nhwc
 from .modules.conv2d import check_conv, packed_weight
 
@@ -47,20 +47,18 @@ class GroupNorm(nn.GroupNorm):
     def forward(self, x, silu=None):
         if silu is None:
             silu = self.fuse_silu
-        xh = as_nhwc(x)
-        fresh = ops.groupnorm_stats(xh, self.num_groups)
-        y = ops.groupnorm_apply(
-            xh, self.num_groups, self.eps, self.weight if self.affine else None, self.bias if self.affine else None,
-            fresh, None, 0, ops.MODE_LOCAL, silu=silu,
-        )
+        y = ops.groupnorm_fused(as_nhwc(x), self.num_groups, self.eps, self.weight if self.affine else None,
+                                self.bias if self.affine else None, silu=silu)
         return as_nchw(y)
 
 
 class Linear(nn.Linear):
     supports_fused_epilogue = True
 
-    def forward(self, x, residual=None):
-        return _lin(self, x, residual=residual)
+    def forward(self, x, residual=None, ln=None, want_stats: bool = False):
+        """``ln = (LayerNorm module, RowStats of x)``: x is un-normalised and the LayerNorm is folded into
+        this projection; ``want_stats``: also return the row statistics of the result."""
+        return _lin(self, x, residual=residual, ln=ln, want_stats=want_stats)
 
 
 class LayerNorm(nn.LayerNorm):
@@ -74,6 +72,8 @@ class Attention(nn.Module):
     residual_connection, rescale_output_factor``.  Head dimension 64."""
 
     supports_fused_epilogue = True
+    # forward() accepts ln=(LayerNorm module, RowStats of the un-normalised input) and want_stats
+    supports_layernorm_fold = True
 
     def __init__(self, query_dim: int, heads: int, cross_attention_dim: int | None = None, linear_cls=Linear):
         super().__init__()
@@ -125,17 +125,19 @@ class Attention(nn.Module):
         self._ctx_ref = ctx  # keeps the storage alive, so its address cannot be reused by another tensor
         return self._ctx_kv
 
-    def forward(self, hidden_states, encoder_hidden_states=None, scale: float = 1.0, *args, residual=None, **kwargs):
+    def forward(self, hidden_states, encoder_hidden_states=None, scale: float = 1.0, *args, residual=None, ln=None,
+                want_stats: bool = False, **kwargs):
         if encoder_hidden_states is None:
             if type(self.to_q) is Linear and self.to_q.out_features % 32 == 0:
-                q, kv = qkv_project(self, self.to_q, self._fused_kv(), hidden_states)
+                q, kv = qkv_project(self, self.to_q, self._fused_kv(), hidden_states, ln=ln)
             else:
+                assert ln is None
                 q, kv = _lin(self.to_q, hidden_states), self._project_kv(hidden_states)
         else:
-            q = _lin(self.to_q, hidden_states)
+            q = _lin(self.to_q, hidden_states, ln=ln)
             kv = self.context_kv(encoder_hidden_states)
         o = ops.attention(q, [kv], self.heads)
-        return _finish(self, o, hidden_states, residual)
+        return _finish(self, o, hidden_states, residual, want_stats=want_stats)
 
 
 def silu(x):
@@ -146,17 +148,24 @@ def geglu(h):
     return ops.geglu(h if h.is_contiguous() else h.contiguous())
 
 
-def linear_geglu(layer: nn.Linear, x):
+def linear_geglu(layer: nn.Linear, x, ln=None):
     """GEGLU projection with the gate applied in the GEMM epilogue.  The interleaved copy of
-    the weight is cached on the layer (inference: parameters are frozen)."""
+    the weight is cached on the layer (inference: parameters are frozen).  ``ln = (LayerNorm
+    module, RowStats of x)`` folds that LayerNorm into the projection."""
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    if ln is not None:
+        fold = _folded(layer, "_bxl_geglu_ln", ln[0], layer.weight, layer.bias, interleave=True)
+        y = ops.gemm_fused(x2, None, geglu=True, ln=(ln[1], fold))
+        return y.view(*lead, fold.weight.shape[0] // 2)
     w = layer.weight
     cache = getattr(layer, "_bxl_geglu", None)
     if cache is None or cache[0] != (w.data_ptr(), w._version):
         layer._bxl_geglu = ((w.data_ptr(), w._version), ops.geglu_interleave(w.detach(), None if layer.bias is None else layer.bias.detach()))
     wi, bi = layer._bxl_geglu[1]
-    lead = x.shape[:-1]
-    x2 = x.reshape(-1, x.shape[-1])
-    y = ops.gemm_geglu(x2 if x2.stride(1) == 1 else x2.contiguous(), wi, bi)
+    y = ops.gemm_geglu(x2, wi, bi)
     return y.view(*lead, wi.shape[0] // 2)
 
 
@@ -174,4 +183,5 @@ class KernelLayers:
     upsample2x = staticmethod(upsample2x)
     memory_format = torch.channels_last
     batched_time_projection = True   # all residual blocks' time-embedding projections in one GEMM
+    fold_layernorm = True            # LayerNorm -> Linear pairs run as one GEMM on the un-normalised input
     linear = staticmethod(lambda x, w, b=None: ops.linear(x, w, b))

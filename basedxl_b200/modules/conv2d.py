@@ -68,7 +68,20 @@ class BasedConv2dPP(BaseModule):
         y = ops.conv3x3(body, packed_weight(m), m.bias, stride=stride, top=top, bot=bot, **fused)
         return as_nchw(y)
 
-    def forward(self, x: torch.Tensor, *args, bias_rows=None, residual=None, **kwargs) -> torch.Tensor:
+    def halo_staging(self) -> torch.Tensor | None:
+        """This strip's staging range ``[2, B, pad, W, C]`` when the next call is a displaced step, so
+        that the producer of the input can write the boundary rows there itself (``forward`` is then
+        called with ``halo_packed=True``); None when the layer packs them itself."""
+        cfg = self.basedxl_config
+        if (cfg.n_device_per_batch == 1 or self.is_first_layer or self.comm_manager is None or self.idx is None
+                or self.comm_manager.buffer_list is None or self.counter <= cfg.warmup_steps or self.module.padding[0] != 1):
+            return None
+        # the gather of the previous step that still reads this range must have finished
+        self._wait_pending()
+        shape = self.comm_manager.shapes[self.idx]  # registered as [2, B, C, pad, W]
+        return self.comm_manager.own_slot(self.idx).view(2, shape[1], shape[3], shape[4], shape[2])
+
+    def forward(self, x: torch.Tensor, *args, bias_rows=None, residual=None, halo_packed: bool = False, **kwargs) -> torch.Tensor:
         torch.cuda.nvtx.range_push("conv2d::forward")
         cfg = self.basedxl_config
         m = self.module
@@ -111,7 +124,8 @@ class BasedConv2dPP(BaseModule):
                     assert self.comm_manager is not None
                     # pack straight into the own staging range, then queue it
                     own = self.comm_manager.own_slot(self.idx)
-                    ops.halo_pack(xh, pad, out=own.view(2, b, pad, w, c))
+                    if not halo_packed:
+                        ops.halo_pack(xh, pad, out=own.view(2, b, pad, w, c))
                     self.comm_manager.enqueue(self.idx, own)
 
         self.counter += 1

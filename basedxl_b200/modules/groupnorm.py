@@ -23,7 +23,11 @@ class BasedXLGroupNorm(BaseModule):
         assert isinstance(module, nn.GroupNorm)
         super().__init__(module, basedxl_config)
 
-    def forward(self, x: torch.Tensor, silu: bool | None = None) -> torch.Tensor:
+    # forward() can also write the first and last row of its result into the staging range of the
+    # convolution that consumes it (what that convolution publishes to the neighbouring strips)
+    supports_halo_out = True
+
+    def forward(self, x: torch.Tensor, silu: bool | None = None, halo_out: torch.Tensor | None = None) -> torch.Tensor:
         torch.cuda.nvtx.range_push("group_norm::forward")
         m = self.module
         cfg = self.basedxl_config
@@ -44,18 +48,26 @@ class BasedXLGroupNorm(BaseModule):
                 self.buffer_list = [t.view(-1).view(torch.float32) for t in self.comm_manager.get_buffer_list(self.idx)]
 
         xh = as_nhwc(x)
-        fresh = ops.groupnorm_stats(xh, groups)  # [2, B, G] fp32
         gamma = m.weight if m.affine else None
         beta = m.bias if m.affine else None
         if self.buffer_list is None:
-            y = ops.groupnorm_apply(xh, groups, m.eps, gamma, beta, fresh, None, 0, ops.MODE_LOCAL, silu=silu)
+            # strip statistics only: one launch
+            y = ops.groupnorm_fused(xh, groups, m.eps, gamma, beta, silu=silu, halo_out=halo_out)
         elif self.counter <= cfg.warmup_steps:
+            # synchronous step: the fresh moments of all strips are gathered between the two passes
+            fresh = ops.groupnorm_stats(xh, groups)  # [2, B, G] fp32
             dist.all_gather(self.buffer_list, fresh.view(-1), group=cfg.batch_group, async_op=False)
             y = ops.groupnorm_apply(xh, groups, m.eps, gamma, beta, fresh, self.buffer_list, cfg.split_idx(), ops.MODE_SYNC, silu=silu)
+            if halo_out is not None:
+                ops.halo_pack(y, 1, out=halo_out)
         else:
-            y = ops.groupnorm_apply(xh, groups, m.eps, gamma, beta, fresh, self.buffer_list, cfg.split_idx(), ops.MODE_STALE, silu=silu)
+            # displaced step: one launch; the kernel reads every strip's stale moments (its own
+            # included) and then stores its fresh moments straight into its own staging range
             assert self.comm_manager is not None
-            self.comm_manager.enqueue(self.idx, fresh.view(-1))
+            own = self.buffer_list[cfg.split_idx()]
+            y = ops.groupnorm_fused(xh, groups, m.eps, gamma, beta, self.buffer_list, cfg.split_idx(), ops.MODE_STALE, silu=silu,
+                                    fresh_out=own.view(2, n, groups), halo_out=halo_out)
+            self.comm_manager.enqueue(self.idx, own)
         self.counter += 1
         torch.cuda.nvtx.range_pop()
         return as_nchw(y)

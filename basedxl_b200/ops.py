@@ -353,6 +353,32 @@ def groupnorm_apply(x, groups, eps, gamma, beta, fresh, peers=None, own=0, mode=
     return out
 
 
+def groupnorm_fused(x, groups, eps, gamma, beta, peers=None, own=0, mode=MODE_LOCAL, silu=False, fresh_out=None, halo_out=None, out=None):
+    """GroupNorm (+ SiLU) of an NHWC strip in one launch (``MODE_LOCAL`` or ``MODE_STALE``).
+    ``fresh_out`` ([2, B, G] fp32) receives the strip's moments - it may be the strip's own entry of
+    ``peers``; ``halo_out`` ([2, B, 1, W, C] fp16) receives the first and last row of the result."""
+    _nhwc_strip(x, "x")
+    _req(mode in (MODE_LOCAL, MODE_STALE), "groupnorm_fused: local or stale moments only")
+    B, H, W, Ci = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    _req(out.shape == x.shape and out.stride() == x.stride(), "groupnorm_fused: output must match x")
+    if fresh_out is not None:
+        _req(fresh_out.dtype == torch.float32 and fresh_out.numel() == 2 * B * groups and fresh_out.is_contiguous(), "groupnorm_fused: bad fresh_out")
+    if halo_out is not None:
+        _f16_cuda(halo_out, "halo_out")
+        _req(halo_out.numel() == 2 * B * W * Ci and halo_out.is_contiguous(), "groupnorm_fused: bad halo_out")
+    n = 0 if peers is None or mode == MODE_LOCAL else len(peers)
+    arr = (_vp * max(n, 1))(*([_p(t) for t in peers] if n else [None]))
+    l = _lib.lib()
+    _lib.check(
+        l.bxl_groupnorm_fused_f16(_p(x), _p(out), x.stride(0), B, H, W, Ci, groups, _p(fresh_out), arr, n, own, mode, float(eps),
+                                  _p(gamma), _p(beta), int(silu), _p(halo_out), _stream()),
+        l,
+    )
+    return out
+
+
 # --------------------------------------------------------------------------- attention
 def attention(q, kv_slots, heads: int, scale: float | None = None, out=None):
     """``q [B, L_q, C]`` against the concatenation of ``kv_slots`` (each

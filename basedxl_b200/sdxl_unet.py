@@ -100,27 +100,34 @@ class ResnetBlock2D(nn.Module):
             if _fused(n):
                 n.fuse_silu = True
 
-    def _norm_act(self, norm, x):
+    def _norm_act(self, norm, x, conv=None):
+        """norm + SiLU.  Returns (h, halo_packed): where the norm can write boundary rows and the
+        convolution that consumes ``h`` offers its staging range, the rows ``conv`` publishes to the
+        neighbouring strips are written by the norm's kernel."""
         # the swap may have wrapped the norm: the wrapper reads fuse_silu off the wrapped module
         inner = getattr(norm, "module", norm)
         if _fused(norm) and getattr(inner, "fuse_silu", False):
-            return norm(x)
-        return self.L.silu(norm(x))
+            staging = getattr(conv, "halo_staging", None)
+            halo = staging() if staging is not None and getattr(norm, "supports_halo_out", False) else None
+            if halo is not None:
+                return norm(x, halo_out=halo), True
+            return norm(x), False
+        return self.L.silu(norm(x)), False
 
     def forward(self, x, temb_act):
         """``temb_act`` = SiLU(time embedding) [B, temb_dim]."""
-        h = self._norm_act(self.norm1, x)
+        h, packed1 = self._norm_act(self.norm1, x, self.conv1)
         t, self.t_pre = self.t_pre, None
         if t is None:
             t = self.time_emb_proj(temb_act)  # [B, cout]
         if _fused(self.conv1):
-            h = self.conv1(h, bias_rows=t)
+            h = self.conv1(h, bias_rows=t, halo_packed=True) if packed1 else self.conv1(h, bias_rows=t)
         else:
             h = self.conv1(h) + t[:, :, None, None]
-        h = self._norm_act(self.norm2, h)
+        h, packed2 = self._norm_act(self.norm2, h, self.conv2)
         sc = x if self.conv_shortcut is None else self.conv_shortcut(x)
         if _fused(self.conv2):
-            return self.conv2(h, residual=sc)
+            return self.conv2(h, residual=sc, halo_packed=True) if packed2 else self.conv2(h, residual=sc)
         return self.conv2(h) + sc
 
 
@@ -131,9 +138,16 @@ class FeedForward(nn.Module):
         self.proj = L.Linear(dim, dim * 8)   # GEGLU: value and gate halves, 4*dim each
         self.out = L.Linear(dim * 4, dim)
 
-    def forward(self, x, residual):
+    def forward(self, x, residual, ln=None, want_stats: bool = False):
+        """``ln = (LayerNorm module, row statistics of x)``: ``x`` is un-normalised and the LayerNorm is
+        folded into the projection; ``want_stats``: also return the row statistics of the result."""
         fused_proj = getattr(self.L, "linear_geglu", None)
-        h = fused_proj(self.proj, x) if fused_proj is not None and type(self.proj) is self.L.Linear else self.L.geglu(self.proj(x))
+        if ln is not None:
+            h = fused_proj(self.proj, x, ln=ln)
+        else:
+            h = fused_proj(self.proj, x) if fused_proj is not None and type(self.proj) is self.L.Linear else self.L.geglu(self.proj(x))
+        if want_stats:
+            return self.out(h, residual=residual, want_stats=True)
         if _fused(self.out):
             return self.out(h, residual=residual)
         return self.out(h) + residual
@@ -142,6 +156,7 @@ class FeedForward(nn.Module):
 class BasicTransformerBlock(nn.Module):
     def __init__(self, L, dim: int, heads: int, cross_dim: int):
         super().__init__()
+        self.L = L
         self.norm1 = L.LayerNorm(dim)
         self.attn1 = L.Attention(dim, heads)
         self.norm2 = L.LayerNorm(dim)
@@ -155,10 +170,30 @@ class BasicTransformerBlock(nn.Module):
             return attn(x, encoder_hidden_states=ctx, residual=residual)
         return attn(x, encoder_hidden_states=ctx) + residual
 
-    def forward(self, h, ctx):
-        h = self._attn(self.attn1, self.norm1(h), None, h)
-        h = self._attn(self.attn2, self.norm2(h), ctx, h)
-        return self.ff(self.norm3(h), residual=h)
+    def folds_layernorm(self) -> bool:
+        """Whether the three LayerNorms of this block can run inside the projections that consume
+        them (the layer factory offers it and no projection has been swapped for another type)."""
+        L = self.L
+        if not getattr(L, "fold_layernorm", False):
+            return False
+        from .modules.attn import attention_supports_folding, can_fold_layernorm
+
+        a1, a2 = getattr(self.attn1, "module", self.attn1), getattr(self.attn2, "module", self.attn2)
+        return (attention_supports_folding(self.attn1) and attention_supports_folding(self.attn2)
+                and can_fold_layernorm(self.norm1, a1.to_q, a1.to_k, a1.to_v) and can_fold_layernorm(self.norm2, a2.to_q)
+                and can_fold_layernorm(self.norm3, self.ff.proj) and type(self.ff.proj) is L.Linear and type(self.ff.out) is L.Linear)
+
+    def forward(self, h, ctx, stats=None, want_stats: bool = False):
+        """``stats``: row statistics of ``h`` left by the GEMM that produced it.  When given, no
+        LayerNorm kernel runs: every projection takes the un-normalised rows plus their statistics,
+        and every GEMM that closes a residual branch emits the statistics for the next one."""
+        if stats is None:
+            h = self._attn(self.attn1, self.norm1(h), None, h)
+            h = self._attn(self.attn2, self.norm2(h), ctx, h)
+            return self.ff(self.norm3(h), residual=h)
+        h, stats = self.attn1(h, encoder_hidden_states=None, residual=h, ln=(self.norm1, stats), want_stats=True)
+        h, stats = self.attn2(h, encoder_hidden_states=ctx, residual=h, ln=(self.norm2, stats), want_stats=True)
+        return self.ff(h, residual=h, ln=(self.norm3, stats), want_stats=want_stats)
 
 
 class Transformer2DModel(nn.Module):
@@ -174,9 +209,18 @@ class Transformer2DModel(nn.Module):
         # channels-last image <-> token matrix is a view
         tokens = lambda t: t.permute(0, 2, 3, 1).reshape(b, hh * ww, c)
         res = tokens(x)
-        h = self.proj_in(tokens(self.norm(x)))
-        for blk in self.transformer_blocks:
-            h = blk(h, ctx)
+        blocks = list(self.transformer_blocks)
+        if blocks and type(self.proj_in) is getattr(blocks[0].L, "Linear", None) and all(blk.folds_layernorm() for blk in blocks):
+            # LayerNorms folded into the projections: proj_in emits the first row statistics
+            h, stats = self.proj_in(tokens(self.norm(x)), want_stats=True)
+            for i, blk in enumerate(blocks):
+                last = i == len(blocks) - 1
+                out = blk(h, ctx, stats=stats, want_stats=not last)
+                h, stats = (out, None) if last else out
+        else:
+            h = self.proj_in(tokens(self.norm(x)))
+            for blk in blocks:
+                h = blk(h, ctx)
         if _fused(self.proj_out):
             h = self.proj_out(h, residual=res)
         else:

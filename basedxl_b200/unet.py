@@ -91,6 +91,9 @@ class BasedXLUnet(BaseModel):
         ~1200 kernels from Python.  Single-GPU runs capture the whole forward."""
         self.cuda_graph = enabled
         self.release_graph()
+        for m in self.model.modules():
+            if isinstance(m, BasedXLCrossAttentionPP):
+                m.kv_managed = bool(enabled)
 
     def release_graph(self):
         """Drop the captured step graph (call before destroying the process group)."""
@@ -164,11 +167,17 @@ class BasedXLUnet(BaseModel):
 
     @torch.no_grad()
     def _refresh_context(self, sample, timestep, encoder_hidden_states, added_cond_kwargs):
-        """Recompute, in place, the conditioning K/V that un-patched cross-attention layers cache."""
+        """Recompute, in place, the K/V of the conditioning that cross-attention layers cache (the
+        step graphs read it but do not recompute it)."""
         _, _, ehs, _ = self._slice_batch(sample, timestep, encoder_hidden_states, added_cond_kwargs)
         ctx = ehs.to(next(self.model.parameters()).dtype)
+        wrapped = set()
         for m in self.model.modules():
-            if hasattr(m, "context_kv") and getattr(m, "is_cross", False):
+            if isinstance(m, BasedXLCrossAttentionPP):
+                m.refresh_context_kv(ctx)
+                wrapped.add(id(m.module))
+        for m in self.model.modules():
+            if hasattr(m, "context_kv") and getattr(m, "is_cross", False) and id(m) not in wrapped:
                 m.context_kv(ctx, force=True)
 
     def _slice_batch(self, sample, timestep, encoder_hidden_states, added_cond_kwargs):
@@ -252,12 +261,13 @@ class BasedXLUnet(BaseModel):
             else:
                 output = self.model(sample, timestep, encoder_hidden_states, added_cond_kwargs=added_cond_kwargs, return_dict=False)[0]
         else:
-            # Every step but the first of an image repeats one of two launch sequences: the
-            # synchronous one (steps 1..warmup_steps: blocking per-layer collectives) and the
-            # displaced one (later steps).  Each is captured once - kernels and collectives -
-            # and replayed.  Step 0 runs eagerly: it also refreshes the cross-attention K/V.
+            # Every step of an image repeats one of two launch sequences: the synchronous one (steps
+            # 0..warmup_steps: blocking per-layer collectives) and the displaced one (later steps).
+            # Each is captured once - kernels and collectives - and replayed.  The K/V of the
+            # conditioning, which the reference recomputes in the first step of an image, is
+            # refreshed outside the graphs whenever the conditioning changes.
             c = self.counter
-            graphable = self.cuda_graph and isinstance(timestep, torch.Tensor) and (c > 0 or not self.patched)
+            graphable = self.cuda_graph and isinstance(timestep, torch.Tensor)
             if graphable:
                 from .graph import GraphedStep
 

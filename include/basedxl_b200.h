@@ -206,6 +206,23 @@ int bxl_groupnorm_apply_f16(const void* x, void* y, long long img_stride, int B,
                             const float* fresh_moments, const float* const* peer_moments, int n_peers, int own, int mode,
                             float eps, const void* gamma, const void* beta, int silu, void* stream);
 
+/* GroupNorm (+ SiLU) in ONE launch for the local (mode 0) and stale (mode 2) cases: a cluster of
+ * thread blocks per (image, run of whole groups) reads the strip x[B,H,W,C] once, keeps it in
+ * shared memory while the group sums are exchanged inside the cluster, and normalises it from
+ * there.  Same arithmetic as bxl_groupnorm_stats_f16 followed by bxl_groupnorm_apply_f16.
+ * fresh_out (or NULL): [2][B][G] fp32 moments of this strip; it may be the strip's own entry of
+ * peer_moments (its staging range): the stale values are read before the fresh ones are stored.
+ * halo_out (or NULL): [2][B][W][C] fp16, the first and the last pixel row of y - the rows the
+ * 3x3 convolution that consumes y publishes to the neighbouring strips (conv2d.py:92).
+ * The synchronous mode (fresh moments of all strips) needs a collective between the two passes
+ * and stays on the two-launch form.
+ * Replaces: BasedXLGroupNorm.forward (basedxl/modules/groupnorm.py:38-69) without a collective,
+ * the staging copy of its moments and of the following convolution's boundary rows
+ * (basedxl/utils.py:156). */
+int bxl_groupnorm_fused_f16(const void* x, void* y, long long img_stride, int B, int H, int W, int C, int G,
+                            float* fresh_out, const float* const* peer_moments, int n_peers, int own, int mode, float eps,
+                            const void* gamma, const void* beta, int silu, void* halo_out, void* stream);
+
 /* ---- attention ---------------------------------------------------------------- */
 
 /* out[b, l, h*64 + d] = softmax_l'(q . k * scale) v over the concatenation of

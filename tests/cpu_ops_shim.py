@@ -120,6 +120,16 @@ def groupnorm_apply(x, groups, eps, gamma, beta, fresh, peers=None, own=0, mode=
     return y
 
 
+def groupnorm_fused(x, groups, eps, gamma, beta, peers=None, own=0, mode=MODE_LOCAL, silu=False, fresh_out=None, halo_out=None, out=None):
+    fresh = groupnorm_stats(x, groups)
+    y = groupnorm_apply(x, groups, eps, gamma, beta, fresh, peers, own, mode, silu=silu, out=out)
+    if fresh_out is not None:
+        fresh_out.copy_(fresh.view(fresh_out.shape))  # after the stale values have been used
+    if halo_out is not None:
+        halo_out.copy_(torch.stack([y[:, :1], y[:, -1:]], dim=0).reshape(halo_out.shape))
+    return y
+
+
 def attention(q, kv_slots, heads, scale=None, out=None):
     y = po._sdpa_heads(q, torch.cat(list(kv_slots), dim=1), heads)
     if out is not None:
@@ -145,6 +155,6 @@ def install():
     """Replace the kernel wrappers of ``basedxl_b200.ops`` by the functions above."""
     from basedxl_b200 import ops
 
-    for name in ("gemm", "gemm_dual", "gemm_geglu", "conv_weight_pack", "conv3x3", "halo_pack", "groupnorm_stats", "groupnorm_apply", "attention",
+    for name in ("gemm", "gemm_dual", "gemm_geglu", "conv_weight_pack", "conv3x3", "halo_pack", "groupnorm_stats", "groupnorm_apply", "groupnorm_fused", "attention",
                  "upsample2x", "layernorm", "geglu"):
         setattr(ops, name, globals()[name])

@@ -245,3 +245,80 @@ def test_static_weights_mode_chain():
     finally:
         _lib.check(l.bxl_set_static_weights(0), l, kernels=0)
     assert_close(y, ref, what="gemm chain with static weights")
+
+
+# ---------------------------------------------------------------------------------------------
+# LayerNorm folded into the consumer GEMM, row statistics emitted by the producer GEMM
+# ---------------------------------------------------------------------------------------------
+def _ln_case(M, K, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = h16(torch.randn(M, K, generator=g) * 1.7 + 0.4)
+    gamma, beta = h16(1.0 + 0.2 * torch.randn(K, generator=g)), h16(0.2 * torch.randn(K, generator=g))
+    return g, x, gamma, beta
+
+
+@pytest.mark.parametrize("bn,split,pair", [(0, 0, -1), (64, 1, 0), (128, 2, 0), (256, 4, 0), (128, 1, 1), (160, 1, 0)])
+@pytest.mark.parametrize("M,K,N", [(300, 1280, 1280), (1024, 640, 640)])
+def test_row_statistics_of_the_output(M, K, N, bn, split, pair):
+    """Producer side: per-row (sum, sum of squares) partials of the fp16 output, whatever the tiling."""
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    g, a, _, _ = _ln_case(M, K, M + N + bn + split)
+    w = h16(torch.randn(N, K, generator=g) / K**0.5)
+    bias, res = h16(torch.randn(N, generator=g)), h16(torch.randn(M, N, generator=g))
+    l = _lib.lib()
+    _lib.check(l.bxl_debug_force_tiles(bn, split, pair), l, kernels=0)
+    try:
+        y, st = ops.gemm_fused(a.half().to(dev), w.half().to(dev), bias=bias.half().to(dev), residual=res.half().to(dev), want_stats=True)
+        _lib.device_status()
+    finally:
+        _lib.check(l.bxl_debug_force_tiles(0, 0, -1), l, kernels=0)
+    assert_close(y, a @ w.t() + bias + res, what="gemm with statistics")
+    mean, var = st.moments(N)
+    yf = y.float().cpu()
+    assert_close(mean, yf.mean(dim=1), tol=1e-4, what="row mean of the stored values")
+    assert_close(var, yf.var(dim=1, unbiased=False), tol=1e-3, what="row variance of the stored values")
+
+
+@pytest.mark.parametrize("bn,split,pair", [(0, 0, -1), (96, 1, 0), (128, 2, 0), (256, 4, 0), (128, 1, 1)])
+@pytest.mark.parametrize("kind", ["plain", "dual", "geglu"])
+def test_layernorm_folded_into_gemm(kind, bn, split, pair):
+    """Linear(LayerNorm(x)) computed from the un-normalised x: weight pre-scaled by the gain,
+    rstd * (acc - mean * colsum) + (W beta + b) in the epilogue; the three epilogue forms that
+    follow a LayerNorm in a transformer block."""
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    M, K, N = 520, 1280, 1280
+    g, x, gamma, beta = _ln_case(M, K, 17 + bn + split)
+    # x itself is produced by a GEMM with a residual, which also emits its row statistics
+    a0 = h16(torch.randn(M, 320, generator=g))
+    w0 = h16(torch.randn(K, 320, generator=g) / 320**0.5)
+    xd, st = ops.gemm_fused(a0.half().to(dev), w0.half().to(dev), residual=x.half().to(dev), want_stats=True)
+    x_ref = xd.float().cpu()  # the fp16 values the consumer reads
+    n_w = 2 * N if kind == "geglu" else (3 * N if kind == "dual" else N)
+    w = h16(torch.randn(n_w, K, generator=g) / K**0.5)
+    b = h16(0.3 * torch.randn(n_w, generator=g))
+    ln = torch.nn.functional.layer_norm(x_ref, (K,), gamma, beta, 1e-5)
+    l = _lib.lib()
+    _lib.check(l.bxl_debug_force_tiles(bn, split, pair), l, kernels=0)
+    try:
+        if kind == "geglu":
+            wi, bi = ops.geglu_interleave(w.half().to(dev), b.half().to(dev))
+            fold = ops.FoldedLayerNorm(wi, bi, gamma.half().to(dev), beta.half().to(dev), 1e-5)
+            y = ops.gemm_fused(xd, None, geglu=True, ln=(st, fold))
+            h = ln @ w.t() + b
+            ref = h[:, :N] * torch.nn.functional.gelu(h[:, N:])
+        elif kind == "dual":
+            fold = ops.FoldedLayerNorm(w.half().to(dev), b.half().to(dev), gamma.half().to(dev), beta.half().to(dev), 1e-5)
+            big = torch.zeros(M, 3 * N, device=dev, dtype=torch.float16)
+            q, kv = ops.gemm_fused(xd, None, n_split=N, out2=big[:, N:], ln=(st, fold))
+            y = torch.cat([q, big[:, N:]], dim=1)
+            ref = ln @ w.t() + b
+        else:
+            fold = ops.FoldedLayerNorm(w.half().to(dev), b.half().to(dev), gamma.half().to(dev), beta.half().to(dev), 1e-5)
+            y = ops.gemm_fused(xd, None, ln=(st, fold))
+            ref = ln @ w.t() + b
+        _lib.device_status()
+    finally:
+        _lib.check(l.bxl_debug_force_tiles(0, 0, -1), l, kernels=0)
+    assert_close(y, ref, what=f"LayerNorm folded into {kind} GEMM (bn={bn} split={split} pair={pair})")
