@@ -16,7 +16,7 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libbasedxl_b200.so")
-SOURCES = ["bxl_host.cu", "gemm_conv.cu", "groupnorm.cu", "attention.cu", "elementwise.cu"]
+SOURCES = ["bxl_host.cu", "gemm_conv.cu", "groupnorm.cu", "attention.cu", "elementwise.cu", "comm.cu"]
 HEADERS = ["bxl_common.cuh", "bxl_host.h", os.path.join("..", "..", "include", "basedxl_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

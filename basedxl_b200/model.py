@@ -89,15 +89,18 @@ class BasedXLPipeline:
         if fused:
             from . import ops
 
-            latents = latents.contiguous().clone()  # updated in place by the fused step
-            x2 = torch.empty((2, *latents.shape[1:]), device=latents.device, dtype=dt)
+            # channels-last throughout: the UNet produces its output in that order (and every strip's
+            # rows are then one contiguous range), so the fused update reads it as it is
+            cl = torch.channels_last
+            latents = latents.contiguous(memory_format=cl).clone()  # updated in place by the fused step
+            x2 = torch.empty((2, *latents.shape[1:]), device=latents.device, dtype=dt, memory_format=cl)
             x = sch.scale_model_input(latents, first_step).to(dt)
             x2[0:1], x2[1:2] = x, x
         for i in range(first_step, last_step):
             if fused:
                 eps = self.unet(x2, sch.timesteps[i], ehs, added_cond_kwargs=added)[0]
                 # guidance + Euler update + scaling of the next input: one kernel
-                ops.cfg_euler_step(eps.contiguous(), latents, x2, guidance_scale, sch.sigmas[i], sch.sigmas[i + 1])
+                ops.cfg_euler_step(eps.contiguous(memory_format=cl), latents, x2, guidance_scale, sch.sigmas[i], sch.sigmas[i + 1])
             else:
                 x = sch.scale_model_input(latents, i).to(dt)
                 eps = self.unet(torch.cat([x, x]), sch.timesteps[i], ehs, added_cond_kwargs=added)[0].float()

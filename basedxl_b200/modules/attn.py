@@ -17,7 +17,6 @@ from __future__ import annotations
 
 import torch
 import torch.nn as nn
-from torch import distributed as dist
 
 from .. import ops
 from ..utils import BasedXLConfig
@@ -211,9 +210,11 @@ class BasedXLSelfAttentionPP(BasedXLAttentionPP):
         n, idx = cfg.n_device_per_batch, cfg.split_idx()
         b, l, c = hidden_states.shape
         fusable = isinstance(attn.to_q, nn.Linear) and c % 32 == 0
-        if n > 1 and self.buffer_list is not None and self.counter > cfg.warmup_steps:
-            # displaced step: fresh K/V is produced directly in the own staging slot; peers' slots
-            # are one step stale (attn.py:138-141)
+        if n > 1 and self.buffer_list is not None:
+            # fresh K/V is produced directly in the own staging slot (no concatenation, no staging
+            # copy).  Synchronous step: it then goes to every peer and theirs arrive here before the
+            # attention runs (attn.py:134-136); displaced step: the peers' slots are one step stale
+            # and the fresh slot is queued for the asynchronous gather (attn.py:138-141).
             own = self.buffer_list[idx]
             if fusable:
                 q, _ = qkv_project(self, attn.to_q, self.to_kv, hidden_states, kv_out=own.view(b * l, -1), ln=ln)
@@ -222,22 +223,23 @@ class BasedXLSelfAttentionPP(BasedXLAttentionPP):
                 q = _lin(attn.to_q, hidden_states)
                 _lin(self.to_kv, hidden_states, out=own.view(b * l, -1))
             slots = list(self.buffer_list)
-            self.comm_manager.enqueue(self.idx, own)
+            if self.counter <= cfg.warmup_steps:
+                self.comm_manager.sync_exchange(self.idx)
+                own = None
         else:
+            own = None
             if fusable:
                 q, kv = qkv_project(self, attn.to_q, self.to_kv, hidden_states, ln=ln)
             else:
                 assert ln is None
                 q, kv = _lin(attn.to_q, hidden_states), _lin(self.to_kv, hidden_states)
-            if n == 1:
-                slots = [kv]
-            elif self.buffer_list is None:
-                # no staging buffers yet: own K/V stands in for every strip (attn.py:132-133)
-                slots = [kv] * n
-            else:
-                dist.all_gather(self.buffer_list, kv, group=cfg.batch_group, async_op=False)
-                slots = list(self.buffer_list)
+            # one strip, or no staging buffers yet: own K/V stands in for every strip (attn.py:132-133)
+            slots = [kv] * n
         o = ops.attention(q, slots, attn.heads)
+        if own is not None:
+            # queued only now: a gather that this call triggers is ordered after the attention
+            # kernel, which still reads the peers' stale slots in place
+            self.comm_manager.enqueue(self.idx, own)
         return _finish(attn, o, hidden_states, residual, want_stats=want_stats)
 
     def forward(self, hidden_states, encoder_hidden_states=None, scale: float = 1.0, *args, residual=None, ln=None,

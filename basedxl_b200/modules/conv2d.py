@@ -12,7 +12,6 @@ same number of elements is registered here but stored as ``[2, B, pad, W, C]``
 from __future__ import annotations
 
 import torch
-from torch import distributed as dist
 from torch import nn
 
 from .. import ops
@@ -113,8 +112,10 @@ class BasedConv2dPP(BaseModule):
                 idx, n = cfg.split_idx(), cfg.n_device_per_batch
                 sync = self.counter <= cfg.warmup_steps
                 if sync:
-                    boundary = ops.halo_pack(xh, pad)
-                    dist.all_gather(self.buffer_list, boundary.view(self.buffer_list[0].shape), group=cfg.batch_group, async_op=False)
+                    # fresh boundary rows into the own staging range, then to every peer
+                    assert self.comm_manager is not None
+                    ops.halo_pack(xh, pad, out=self.comm_manager.own_slot(self.idx).view(2, b, pad, w, c))
+                    self.comm_manager.sync_exchange(self.idx)
                 # strip above publishes its bottom rows (index 1), strip below its top rows (index 0)
                 top = self.buffer_list[idx - 1].view(2, b, pad, w, c)[1] if idx > 0 else None
                 bot = self.buffer_list[idx + 1].view(2, b, pad, w, c)[0] if idx < n - 1 else None

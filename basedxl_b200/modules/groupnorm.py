@@ -10,7 +10,6 @@ slots of the shared staging buffer, i.e. the registered shape is
 from __future__ import annotations
 
 import torch
-from torch import distributed as dist
 from torch import nn
 
 from .. import ops
@@ -55,8 +54,9 @@ class BasedXLGroupNorm(BaseModule):
             y = ops.groupnorm_fused(xh, groups, m.eps, gamma, beta, silu=silu, halo_out=halo_out)
         elif self.counter <= cfg.warmup_steps:
             # synchronous step: the fresh moments of all strips are gathered between the two passes
-            fresh = ops.groupnorm_stats(xh, groups)  # [2, B, G] fp32
-            dist.all_gather(self.buffer_list, fresh.view(-1), group=cfg.batch_group, async_op=False)
+            assert self.comm_manager is not None
+            fresh = ops.groupnorm_stats(xh, groups, out=self.buffer_list[cfg.split_idx()].view(2, n, groups))  # own range, fp32
+            self.comm_manager.sync_exchange(self.idx)
             y = ops.groupnorm_apply(xh, groups, m.eps, gamma, beta, fresh, self.buffer_list, cfg.split_idx(), ops.MODE_SYNC, silu=silu)
             if halo_out is not None:
                 ops.halo_pack(y, 1, out=halo_out)

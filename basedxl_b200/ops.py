@@ -441,12 +441,15 @@ def geglu(h):
 
 def cfg_euler_step(eps, latents, next_input, guidance: float, sigma: float, sigma_next: float):
     """Guidance combine, Euler update of ``latents`` (fp32, in place) and the scaled fp16 input
-    of the next step (both CFG rows) in one launch."""
+    of the next step (both CFG rows) in one launch.  The three tensors are dense and share one
+    memory order (all row-major, or all channels-last)."""
     _f16_cuda(eps, "eps"), _f16_cuda(next_input, "next_input")
-    _req(latents.is_cuda and latents.dtype == torch.float32 and latents.is_contiguous(), "cfg_euler_step: fp32 contiguous latents")
+    _req(latents.is_cuda and latents.dtype == torch.float32, "cfg_euler_step: fp32 latents")
     n = latents.numel()
-    _req(eps.is_contiguous() and next_input.is_contiguous() and eps.numel() == 2 * n and next_input.numel() == 2 * n,
-         "cfg_euler_step: eps and next_input must be contiguous [2, ...] tensors matching the latents")
+    fmt = torch.contiguous_format if latents.is_contiguous() else torch.channels_last
+    _req(all(t.is_contiguous(memory_format=fmt) for t in (eps, latents, next_input)) and eps.numel() == 2 * n
+         and next_input.numel() == 2 * n and eps.shape[1:] == latents.shape[1:] and next_input.shape[1:] == latents.shape[1:],
+         "cfg_euler_step: eps and next_input must be dense [2, ...] tensors in the memory order of the latents")
     l = _lib.lib()
     _lib.check(l.bxl_cfg_euler_step(_p(eps), _p(latents), _p(next_input), n, float(guidance), float(sigma), float(sigma_next), _stream()), l)
     return latents, next_input

@@ -38,6 +38,8 @@ class BaseModel(nn.Module):
         self.comm_manager = None
         self.buffer_list = None
         self.output_buffer = None
+        self.world_peer = None
+        self.output_views = None
         self.counter = 0
 
     def forward(self, *args, **kwargs):
@@ -197,30 +199,63 @@ class BasedXLUnet(BaseModel):
         s, t, e, a = self._slice_batch(sample, timestep, encoder_hidden_states, added_cond_kwargs)
         return self.model(s, t, e, added_cond_kwargs=a, return_dict=False)[0]
 
-    def _step_multi(self, sample, timestep, encoder_hidden_states, added_cond_kwargs, drain: bool = True):
-        """One step on this rank's strip / CFG half, then the blocking gather of all
-        ranks' output strips (basedxl/unet.py:166-175,185-195).  With ``drain`` the
-        tail of the exchange queue is flushed and every pending gather joined before
-        returning, which makes the step self-contained (what graph replay needs);
-        without it the tail is flushed by the next step's first layer, as in the
-        reference.  Either way every layer sees exactly the previous step's data."""
+    def _prepare_output(self, sample):
+        """The full-size output every rank assembles each step, channels-last (a strip's rows are then
+        one contiguous range), and - where the ranks can write each other's memory - its mapping in
+        every peer, so that the strips are stored straight into place."""
         cfg = self.basedxl_config
         b, c, h, w = sample.shape
-        local = self._run_local(sample, timestep, encoder_hidden_states, added_cond_kwargs).contiguous()
+        dt = next(self.model.parameters()).dtype
+        self.output_buffer = torch.empty((b, c, h, w), device=cfg.device, dtype=dt, memory_format=torch.channels_last)
+        self.world_peer = None
+        self.output_views = None
+        if self.output_buffer.is_cuda:
+            from .peer import make_peer_group
+
+            self.world_peer = make_peer_group(None, cfg.rank, cfg.world_size, cfg.device, verbose=cfg.verbose and cfg.rank == 0)
+            if self.world_peer is not None:
+                flat = self.output_buffer.permute(0, 2, 3, 1).reshape(-1)  # NHWC memory order, a view
+                self.output_views = [v.view(b, h, w, c) for v in self.world_peer.share(flat)]
+                if self.world_peer.failed is not None:
+                    raise RuntimeError(f"mapping the peers' output buffers failed: {self.world_peer.failed!r}")
+
+    def _step_multi(self, sample, timestep, encoder_hidden_states, added_cond_kwargs, drain: bool = True):
+        """One step on this rank's strip / CFG half, then the assembly of all ranks' output strips
+        (basedxl/unet.py:166-175,185-195).  With ``drain`` the tail of the exchange queue is flushed
+        and every pending gather joined before returning, which makes the step self-contained
+        (what graph replay needs); without it the tail is flushed by the next step's first layer,
+        as in the reference.  Either way every layer sees exactly the previous step's data."""
+        cfg = self.basedxl_config
+        b, c, h, w = sample.shape
+        n = cfg.n_device_per_batch
+        hs = h // n
+        local = self._run_local(sample, timestep, encoder_hidden_states, added_cond_kwargs)
+        local = local.permute(0, 2, 3, 1).contiguous()  # [b_local, h/n, w, c]: the kernels' own order, no copy
         if drain and self.comm_manager is not None:
             self.comm_manager.clear()
         if self.output_buffer is None:
-            self.output_buffer = torch.empty((b, c, h, w), device=local.device, dtype=local.dtype)
-        if self.buffer_list is None:
-            self.buffer_list = [torch.empty_like(local) for _ in range(cfg.world_size)]
-        dist.all_gather(self.buffer_list, local, async_op=False)
-        n = cfg.n_device_per_batch
-        if cfg.use_cfg:
-            # first half of the ranks = batch row 0, second half = row 1
-            torch.cat(self.buffer_list[:n], dim=2, out=self.output_buffer[0:1])
-            torch.cat(self.buffer_list[n:], dim=2, out=self.output_buffer[1:2])
+            self._prepare_output(sample)
+        out = self.output_buffer.permute(0, 2, 3, 1)  # [b, h, w, c] view
+        # rank r serves image batch_idx(r) (CFG split) or all images, rows split_idx(r)*hs ...
+        images = [cfg.batch_idx()] if cfg.use_cfg else list(range(b))
+        r0 = cfg.split_idx() * hs
+        if self.world_peer is not None:
+            # every rank stores its strip into every rank's output (its own included): one kernel,
+            # peer stores + flag barrier; the handshake keeps a fast rank from overwriting an output
+            # that a slower rank still reads
+            for k, img in enumerate(images):
+                dsts = [v[img, r0 : r0 + hs] for v in self.output_views]
+                self.world_peer.exchange(local[k], dsts, handshake=True)
         else:
-            torch.cat(self.buffer_list, dim=2, out=self.output_buffer)
+            if self.buffer_list is None:
+                self.buffer_list = [torch.empty_like(local) for _ in range(cfg.world_size)]
+            dist.all_gather(self.buffer_list, local, async_op=False)
+            for r, t in enumerate(self.buffer_list):
+                rr = cfg.split_idx(r) * hs
+                if cfg.use_cfg:
+                    out[cfg.batch_idx(r), rr : rr + hs].copy_(t[0])
+                else:
+                    out[:, rr : rr + hs].copy_(t)
         return self.output_buffer
 
     # ------------------------------------------------------------------ one denoising step
@@ -247,6 +282,8 @@ class BasedXLUnet(BaseModel):
         b, c, h, w = sample.shape
         if self.patched and self.comm_manager is None:
             self.prepare(sample, timestep, encoder_hidden_states, added_cond_kwargs)
+        if cfg.world_size > 1 and self.output_buffer is None:
+            self._prepare_output(sample)  # collectives and memory mapping: never inside a graph capture
 
         if cfg.world_size == 1:
             if self.cuda_graph and isinstance(timestep, torch.Tensor):

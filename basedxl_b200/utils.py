@@ -121,8 +121,13 @@ class PatchParallelismCommManager:
         self.shapes: list = []
         self.idx_queue: list[int] = []
         self.handles: list | None = None
-        # bytes handed to the collective since creation (own contribution only)
+        # bytes handed to the collectives since creation (own contribution only); calls recorded into
+        # a CUDA graph count once, at capture
         self.bytes_sent = 0
+        self.sync_bytes = 0
+        self.flat = None
+        self.peer = None
+        self.peer_flat = None
 
     def register_tensor(self, shape, torch_dtype: torch.dtype, layer_type: str | None = None) -> int:
         if self.torch_dtype is None:
@@ -150,10 +155,24 @@ class PatchParallelismCommManager:
             print(f"Create buffer with {self.numel / 1e6:.3f}M parameters for {len(self.starts)} tensors on each device.")
             for layer_type, numel in self.numel_dict.items():
                 print(f"  {layer_type}: {numel / 1e6:.3f}M parameters")
-        self.buffer_list = [
-            torch.zeros(self.numel, dtype=self.torch_dtype, device=cfg.device) for _ in range(cfg.n_device_per_batch)
-        ]
+        n = cfg.n_device_per_batch
+        # one allocation, one slot of `numel` elements per strip (16-byte aligned slots)
+        assert (self.numel * torch.empty((), dtype=self.torch_dtype).element_size()) % 16 == 0
+        self.flat = torch.zeros(n * self.numel, dtype=self.torch_dtype, device=cfg.device)
+        self.buffer_list = [self.flat[j * self.numel : (j + 1) * self.numel] for j in range(n)]
         self.handles = [None for _ in range(len(self.starts))]
+        # Peers that can write each other's memory exchange the synchronous steps' tensors with one
+        # kernel per layer (peer stores + flag barrier) instead of a blocking collective.
+        self.peer = None
+        self.peer_flat = None
+        if n > 1 and self.flat.is_cuda and dist.is_initialized():
+            from .peer import make_peer_group
+
+            self.peer = make_peer_group(cfg.batch_group, cfg.split_idx(), n, cfg.device, verbose=cfg.verbose and cfg.rank == 0)
+            if self.peer is not None:
+                self.peer_flat = self.peer.share(self.flat)
+                if self.peer.failed is not None:
+                    raise RuntimeError(f"mapping the peers' staging buffers failed: {self.peer.failed!r}")
 
     def get_buffer_list(self, idx: int) -> list[torch.Tensor]:
         assert self.buffer_list is not None
@@ -164,6 +183,25 @@ class PatchParallelismCommManager:
         assert self.buffer_list is not None
         own = self.basedxl_config.split_idx()
         return self.buffer_list[own][self.starts[idx] : self.ends[idx]].view(self.shapes[idx])
+
+    def sync_exchange(self, idx: int):
+        """Synchronous steps: this rank's fresh tensor ``idx`` (already written into its own slot)
+        goes to every peer, and the call returns with the stream ordered after the arrival of all
+        the peers' tensors ``idx`` (the blocking all-gathers of basedxl/modules/conv2d.py:95,
+        groupnorm.py:47, attn.py:135)."""
+        assert self.buffer_list is not None
+        cfg = self.basedxl_config
+        own, n = cfg.split_idx(), cfg.n_device_per_batch
+        start, end = self.starts[idx], self.ends[idx]
+        src = self.buffer_list[own][start:end]
+        self.sync_bytes += src.numel() * src.element_size()
+        if self.peer is not None:
+            base = own * self.numel
+            dsts = [None if p == own else self.peer_flat[p][base + start : base + end] for p in range(n)]
+            self.peer.exchange(src, dsts)
+        else:
+            outs = [t[start:end] for t in self.buffer_list]
+            dist.all_gather(outs, src if src.is_cuda else src.clone(), group=cfg.batch_group, async_op=False)
 
     def communicate(self):
         assert self.buffer_list is not None and self.handles is not None

@@ -282,6 +282,33 @@ def workload_name(args) -> str:
             f"50 Euler steps, 5 synchronous steps then displaced")
 
 
+def comm_summary(pipe, cfg, step_ms):
+    """What a rank exchanges per step (bytes from the registered tensors), over which transport,
+    and the measured device time of synchronous and displaced steps."""
+    cm = pipe.unet.comm_manager
+    n = cfg.n_device_per_batch
+    sync_steps = cfg.warmup_steps + 1
+    med = lambda v: round(statistics.median(v), 3) if v else None
+    out = {
+        "output_assembly": "peer stores + flag barrier (bxl_comm_exchange)" if pipe.unet.world_peer is not None else "nccl all_gather",
+        "sync_step_ms": med(step_ms[:sync_steps]), "displaced_step_ms": med(step_ms[sync_steps:]),
+    }
+    if cm is not None and cm.numel:
+        slot = cm.numel * 2  # fp16 staging slot of this rank: halo rows, GroupNorm moments, K/V of all patched layers
+        gathers = -(-len(cm.starts) // cfg.comm_checkpoint)
+        out.update({
+            "strips_per_image": n, "exchanged_tensors": len(cm.starts), "slot_bytes": slot,
+            "displaced_step": {"transport": "nccl all_gather on the communication stream, joined one step later", "gathers": gathers,
+                               "bytes_sent_per_rank": slot, "bytes_received_per_rank": slot * (n - 1)},
+            "sync_step": {"transport": "peer stores + flag barrier, one kernel per layer (bxl_comm_exchange)" if cm.peer is not None
+                          else "blocking nccl all_gather per layer", "exchanges": len(cm.starts), "bytes_pushed_per_rank": slot * (n - 1)},
+        })
+        # NVLink time of the displaced exchange at the measured peer-copy rate, against the step it hides behind
+        nvlink_ms = slot * (n - 1) / 770e9 * 1e3
+        out["displaced_step"]["nvlink_ms_at_770GBps"] = round(nvlink_ms, 3)
+    return out
+
+
 def run_b200_arm(args):
     from basedxl_b200 import _lib
     from basedxl_b200.flops import unet_flops
@@ -346,9 +373,20 @@ def run_b200_arm(args):
     sampler.start()
     ms_total, launches, out = timed_image(lat, ehs, added)
     clocks = sampler.stop()
-    comm0 = pipe.unet.comm_manager.bytes_sent if pipe.unet.comm_manager is not None else 0
     ms_second, _, out2 = timed_image(lat, ehs, added)
-    comm_bytes_image = (pipe.unet.comm_manager.bytes_sent - comm0) if pipe.unet.comm_manager is not None else 0
+    # per-step device times of one more image (diagnostic: synchronous vs displaced steps)
+    step_ms = []
+    if world > 1:
+        pipe.unet.reset()
+        barrier()
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+        cur = lat
+        for i in range(args.steps):
+            evs[i].record(stream)
+            cur = pipe.denoise(cur, ehs, added, steps_total, 5.0, first_step=i, last_step=i + 1)
+        evs[args.steps].record(stream)
+        barrier()
+        step_ms = [evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)]
     _lib.device_status()
     assert torch.isfinite(out).all(), "non-finite latents"
     # the same image twice: the loop (graph replay included) must be deterministic
@@ -407,9 +445,7 @@ def run_b200_arm(args):
             "roofline": roof,
         }
         if world > 1:
-            # own contribution handed to the stale-exchange gathers (displaced steps) per image and rank
-            line["comm"] = {"exchange_bytes_per_rank_per_image": comm_bytes_image, "steps": args.steps,
-                            "note": "asynchronous gathers run on the communication stream and are joined one step later"}
+            line["comm"] = comm_summary(pipe, cfg, step_ms)
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)

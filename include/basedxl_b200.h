@@ -237,6 +237,29 @@ int bxl_attn_fwd_f16(const void* q, long long q_img_stride, long long ld_q, cons
                      long long kv_img_stride, long long ld_kv, int v_col0, void* out, long long out_img_stride,
                      long long ld_out, int B, int heads, int L_q, int L_slot, float scale, void* stream);
 
+/* ---- exchange between strips over peer memory ----------------------------------- */
+
+/* Size of a group's control words (sequence-number flags; see bxl_comm_exchange).  The caller
+ * allocates them ZEROED in memory that every peer of the group can write, one block per rank. */
+long long bxl_comm_ctl_bytes(void);
+
+/* What a blocking all-gather of one contribution per rank does, as ONE kernel over peer memory
+ * (NVLink): copies `nbytes` from `src` (this rank's memory) to peer_dst[p] for every p with a
+ * non-NULL entry (the place of this rank's contribution in peer p's memory, mapped into this
+ * process; entry `own` may be NULL when src already is that place), then meets the peers at a
+ * flag barrier, so that when the kernel ends every peer's contribution has arrived in THIS
+ * rank's memory.  ctl = this rank's control words, peer_ctl[p] = peer p's (mapped); peer_dst and
+ * peer_ctl are HOST arrays of n_peers device pointers.  All ranks of a group launch the same
+ * sequence of exchanges, each rank on one stream.  handshake != 0: first wait until every peer has
+ * reached this exchange, for a destination that the previous exchange of the group also wrote
+ * (the per-step output).  Waits give up after wait_seconds and report through
+ * bxl_device_status() (site 800 + peer: handshake, 900 + peer: arrival).
+ * Replaces: the blocking per-layer dist.all_gather of the synchronous steps
+ * (basedxl/modules/conv2d.py:95, groupnorm.py:47, attn.py:135) and the output gather
+ * (basedxl/unet.py:172,193). */
+int bxl_comm_exchange(const void* src, void* const* peer_dst, long long nbytes, void* ctl, void* const* peer_ctl,
+                      int n_peers, int own, int handshake, double wait_seconds, void* stream);
+
 /* ---- host-graph helpers (the elementwise work between the patched operators) -- */
 
 /* y[B,2H,2W,C] = nearest-neighbour up-sampling of x[B,H,W,C]. */
