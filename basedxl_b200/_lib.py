@@ -54,6 +54,9 @@ SIGNATURES = {
     "bxl_groupnorm_fused_f16": (_i, [_vp, _vp, _ll, _i, _i, _i, _i, _i, _vp, C.POINTER(_vp), _i, _i, _i, _f, _vp, _vp, _i, _vp, _vp]),
     "bxl_attn_fwd_f16": (_i, [_vp, _ll, _ll, C.POINTER(_vp), _i, _ll, _ll, _i, _vp, _ll, _ll, _i, _i, _i, _i, _f, _vp]),
     "bxl_comm_ctl_bytes": (_ll, []),
+    "bxl_comm_ipc_export": (_i, [_vp, C.c_char_p, C.POINTER(_ll)]),
+    "bxl_comm_ipc_open": (_i, [C.c_char_p, C.POINTER(_vp)]),
+    "bxl_comm_ipc_close": (_i, [_vp]),
     "bxl_comm_exchange": (_i, [_vp, C.POINTER(_vp), _ll, _vp, C.POINTER(_vp), _i, _i, _i, C.c_double, _vp]),
     "bxl_upsample2x_f16": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
     "bxl_layernorm_f16": (_i, [_vp, _vp, _vp, _vp, _ll, _i, _f, _vp]),

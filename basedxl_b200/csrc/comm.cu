@@ -122,6 +122,49 @@ using namespace bxl;
 
 extern "C" long long bxl_comm_ctl_bytes(void) { return 32 * sizeof(unsigned); }
 
+// ---- mapping a peer process's buffer (CUDA IPC) --------------------------------------
+typedef CUresult (*GetAddressRangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+
+extern "C" int bxl_comm_ipc_export(const void* ptr, unsigned char* handle64, long long* offset_bytes) {
+  if (!ptr || !handle64 || !offset_bytes) return fail(kErrInvalidArg, "bxl_comm_ipc_export: null argument");
+  static GetAddressRangeFn get_range = nullptr;
+  if (!get_range) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    const cudaError_t e = cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
+      return fail(kErrCuda, "bxl_comm_ipc_export: cuMemGetAddressRange entry point unavailable (%s)", cudaGetErrorString(e));
+    get_range = reinterpret_cast<GetAddressRangeFn>(fn);
+  }
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  const CUresult r = get_range(&base, &size, reinterpret_cast<CUdeviceptr>(ptr));
+  if (r != CUDA_SUCCESS) return fail(kErrCuda, "bxl_comm_ipc_export: cuMemGetAddressRange failed with CUresult %d", (int)r);
+  cudaIpcMemHandle_t h;
+  static_assert(sizeof(h) == 64, "IPC handles are 64 bytes");
+  if (int rc = check_cuda(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base)), "cudaIpcGetMemHandle")) return rc;
+  memcpy(handle64, &h, 64);
+  *offset_bytes = static_cast<long long>(reinterpret_cast<CUdeviceptr>(ptr) - base);
+  return kOk;
+}
+
+extern "C" int bxl_comm_ipc_open(const unsigned char* handle64, void** base_out) {
+  if (!handle64 || !base_out) return fail(kErrInvalidArg, "bxl_comm_ipc_open: null argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void* p = nullptr;
+  // opened with the CURRENT device as the one that will access the memory: peer access between it
+  // and the owning device is switched on as part of the mapping
+  if (int rc = check_cuda(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle")) return rc;
+  *base_out = p;
+  return kOk;
+}
+
+extern "C" int bxl_comm_ipc_close(void* base) {
+  if (!base) return kOk;
+  return check_cuda(cudaIpcCloseMemHandle(base), "cudaIpcCloseMemHandle");
+}
+
 extern "C" int bxl_comm_exchange(const void* src, void* const* peer_dst, long long nbytes, void* ctl, void* const* peer_ctl,
                                  int n_peers, int own, int handshake, double wait_seconds, void* stream) {
   if (n_peers < 1 || n_peers > kCommMaxPeers || own < 0 || own >= n_peers)

@@ -215,7 +215,8 @@ class BasedXLUnet(BaseModel):
             self.world_peer = make_peer_group(None, cfg.rank, cfg.world_size, cfg.device, verbose=cfg.verbose and cfg.rank == 0)
             if self.world_peer is not None:
                 flat = self.output_buffer.permute(0, 2, 3, 1).reshape(-1)  # NHWC memory order, a view
-                self.output_views = [v.view(b, h, w, c) for v in self.world_peer.share(flat)]
+                assert flat.data_ptr() == self.output_buffer.data_ptr()
+                self.output_views = self.world_peer.share(flat)  # address of every rank's output
                 if self.world_peer.failed is not None:
                     raise RuntimeError(f"mapping the peers' output buffers failed: {self.world_peer.failed!r}")
 
@@ -244,8 +245,8 @@ class BasedXLUnet(BaseModel):
             # peer stores + flag barrier; the handshake keeps a fast rank from overwriting an output
             # that a slower rank still reads
             for k, img in enumerate(images):
-                dsts = [v[img, r0 : r0 + hs] for v in self.output_views]
-                self.world_peer.exchange(local[k], dsts, handshake=True)
+                off = ((img * h + r0) * w * c) * local.element_size()  # rows r0.. of image img, NHWC
+                self.world_peer.exchange(local[k], [p + off for p in self.output_views], handshake=True)
         else:
             if self.buffer_list is None:
                 self.buffer_list = [torch.empty_like(local) for _ in range(cfg.world_size)]
@@ -318,8 +319,11 @@ class BasedXLUnet(BaseModel):
                         if isinstance(module, BaseModule):
                             module.set_counter(c)
                     drain = displaced
+                    # patched layers: no rehearsal (see above; their registration pass has already
+                    # built every cached weight copy).  CFG split alone: one eager run first, which
+                    # builds those copies outside the capture and changes no state.
                     setattr(self, slot, GraphedStep(lambda s_, t_, e_, a_, d=drain: self._step_multi(s_, t_, e_, a_, drain=d),
-                                                    warmup_runs=0, on_condition_change=self._refresh_context))
+                                                    warmup_runs=0 if self.patched else 1, on_condition_change=self._refresh_context))
                 output = getattr(self, slot)(sample, timestep, encoder_hidden_states, added_cond_kwargs)
             else:
                 output = self._step_multi(sample, timestep, encoder_hidden_states, added_cond_kwargs, drain=False)

@@ -196,8 +196,8 @@ class PatchParallelismCommManager:
         src = self.buffer_list[own][start:end]
         self.sync_bytes += src.numel() * src.element_size()
         if self.peer is not None:
-            base = own * self.numel
-            dsts = [None if p == own else self.peer_flat[p][base + start : base + end] for p in range(n)]
+            off = (own * self.numel + start) * src.element_size()  # this rank's slot in every member's buffer
+            dsts = [None if p == own else self.peer_flat[p] + off for p in range(n)]
             self.peer.exchange(src, dsts)
         else:
             outs = [t[start:end] for t in self.buffer_list]

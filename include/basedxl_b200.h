@@ -243,6 +243,20 @@ int bxl_attn_fwd_f16(const void* q, long long q_img_stride, long long ld_q, cons
  * allocates them ZEROED in memory that every peer of the group can write, one block per rank. */
 long long bxl_comm_ctl_bytes(void);
 
+/* Mapping a buffer of a peer process (same node) into this one, for bxl_comm_exchange.
+ * bxl_comm_ipc_export: the 64-byte CUDA IPC handle of the allocation that contains `ptr` (any
+ *   cudaMalloc-backed device memory of this process, e.g. a framework tensor) and ptr's offset in it;
+ *   the owner keeps the memory allocated while peers have it open.
+ * bxl_comm_ipc_open: maps that allocation for kernels of the CURRENT device (which also switches on
+ *   peer access between the two devices) and returns its base address in this process; the peer's
+ *   buffer is at base + offset.  An allocation can be opened once per process.
+ * bxl_comm_ipc_close: unmaps it.
+ * The three calls are set-up time; they are the only entry points that touch the address space.
+ * No counterpart in the reference (its collectives leave transport set-up to NCCL). */
+int bxl_comm_ipc_export(const void* ptr, unsigned char* handle64, long long* offset_bytes);
+int bxl_comm_ipc_open(const unsigned char* handle64, void** base_out);
+int bxl_comm_ipc_close(void* base);
+
 /* What a blocking all-gather of one contribution per rank does, as ONE kernel over peer memory
  * (NVLink): copies `nbytes` from `src` (this rank's memory) to peer_dst[p] for every p with a
  * non-NULL entry (the place of this rank's contribution in peer p's memory, mapped into this
