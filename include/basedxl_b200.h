@@ -10,8 +10,9 @@
  *     unless the name says f32; activations are NHWC ("channels last") strips or
  *     [rows, cols] matrices; all strides / leading dimensions are in ELEMENTS
  *   - `stream` is a cudaStream_t passed as void*; calls only enqueue work
- *   - no entry point allocates or frees device memory, none synchronises the
- *     host except bxl_device_status(); workspaces are caller-owned
+ *   - no entry point allocates or frees device memory (bxl_comm_ipc_open / _close map and unmap
+ *     a peer process's allocation, at set-up time), none synchronises the host except
+ *     bxl_device_status(); workspaces are caller-owned
  *   - return value: 0 = ok, negative = error (see bxl_last_error()); exceptions
  *     never cross this boundary
  *   - one host thread per process drives the library
