@@ -276,6 +276,161 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+# --------------------------------------------------------------------------- per-operator workload
+def _chain_us(launch, n_sets: int, reps: int = 5) -> float:
+    """Device time per launch of ``launch(i)``, i cycling through ``n_sets`` operand sets: the chain is captured
+    into a CUDA graph, replayed, and timed with CUDA events on the replaying stream."""
+    stream = torch.cuda.current_stream()
+    for i in range(n_sets):
+        launch(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(n_sets):
+            launch(i)
+    graph.replay()
+    times = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        graph.replay()
+        e1.record(stream)
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3 / n_sets)
+    graph.reset()
+    return statistics.median(times)
+
+
+def _cpu_seconds(fn, reps: int = 2) -> float:
+    fn()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        fn()
+    return (time.perf_counter() - t0) / reps
+
+
+def run_ops_workload(args):
+    """The isolated-operator configurations: the five matmul shapes (fp16 operands and the split-operand fp32
+    product, error against an fp64 product by the reference's error-study method) and the patched operators at
+    2 / 4 / 8 strips (3x3 convolution 2x640x64x64, GroupNorm 2x1280x32x32 with 32 groups, self-attention 10 heads x 64
+    on 2x4096x640; stale = current + N(0, 0.01)); for each the device time of this rank's launch, its rate against
+    the measured peak, and the time of the reference's CPU path (PyTorch operators on the host cores) beside it."""
+    from basedxl_b200 import _lib, ops
+    from oracle import matmul as om
+    from oracle import patched_ops as po
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = load_peaks()
+    torch.set_num_threads(os.cpu_count() or 1)
+    cores = torch.get_num_threads()
+    sets = lambda nbytes: max(4, min(48, (512 << 20) // max(1, nbytes) + 1))
+    out = {"metric": "isolated operator configurations", "workload": "ops", "n_gpus": 1, "dtype": "f16", "data": "synthetic",
+           "peaks": peaks, "cpu_cores": cores,
+           "timing": "device: chains over operand sets > L2 replayed from a CUDA graph, CUDA events; CPU: wall clock, PyTorch fp32 operators"}
+    # ---- matmul shapes
+    mm = []
+    for (M, K, N) in [(8192, 640, 640), (8192, 640, 5120), (2048, 1280, 1280), (2048, 1280, 10240), (16384, 320, 320)]:
+        torch.manual_seed(0)
+        a32, b32 = torch.randn(M, K), torch.randn(K, N)
+        a16, b16 = a32.half(), b32.half()
+        n = sets(2 * (M * K + K * N + M * N))
+        A = [a16.to(dev) for _ in range(n)]
+        Bm = [b16.to(dev) for _ in range(n)]
+        C = [torch.empty(M, N, device=dev, dtype=torch.float16) for _ in range(n)]
+        us16 = _chain_us(lambda i: ops.gemm(A[i], Bm[i], out=C[i], b_is_kn=True), n)
+        y16 = C[0].cpu()
+        del A, Bm, C
+        a32d, b32d = a32.to(dev), b32.to(dev)
+        y32 = ops.gemm_split_f32(a32d, b32d).cpu()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ts = []
+        for _ in range(5):
+            e0.record(); ops.gemm_split_f32(a32d, b32d); e1.record(); e1.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        us32 = statistics.median(ts)
+        exp16, exp32 = om.matmul_fp64(a16, b16), om.matmul_fp64(a32, b32)
+        sub = slice(0, 512)  # the model of the reference's fp16 accumulator is evaluated on a row block
+        e_ref = om.error_table(exp16[sub], om.matmul_fp16_accumulate(a16[sub], b16, block_k=32, model="block"))
+        e_16, e_32 = om.error_table(exp16, y16), om.error_table(exp32, y32)
+        cpu_s = _cpu_seconds(lambda: a32 @ b32)
+        fl = 2.0 * M * N * K
+        mm.append({"M": M, "K": K, "N": N,
+                   "fp16_operands": {"us": round(us16, 2), "tflops": round(fl / us16 / 1e6, 1), "frac_of_burst_peak": round(fl / us16 / 1e6 / peaks["tflops_burst"], 3),
+                                     "max_abs_err": e_16["max"], "l1_err": e_16["l1"], "rel_err_median": e_16["rel_median"]},
+                   "split_fp32_operands": {"us_incl_split_kernels_host_launched": round(us32, 2), "max_abs_err": e_32["max"], "l1_err": e_32["l1"],
+                                           "rel_err_median": e_32["rel_median"]},
+                   "reference_fp16_accumulator_model": {"rows": 512, "max_abs_err": e_ref["max"], "l1_err": e_ref["l1"], "rel_err_median": e_ref["rel_median"]},
+                   "cpu_fp32_matmul_s": round(cpu_s, 4)})
+    out["matmul"] = mm
+    _lib.device_status()
+    # ---- patched operators, per strip count
+    gen = torch.Generator().manual_seed(0)
+    x_c = torch.randn(2, 640, 64, 64, generator=gen).half()
+    w_c = (torch.randn(640, 640, 3, 3, generator=gen) / (9 * 640) ** 0.5).half()
+    b_c = torch.randn(640, generator=gen).half()
+    x_g = torch.randn(2, 1280, 32, 32, generator=gen).half()
+    ga, be = torch.randn(1280, generator=gen).half(), torch.randn(1280, generator=gen).half()
+    q_a, kv_a = torch.randn(2, 4096, 640, generator=gen).half(), torch.randn(2, 4096, 1280, generator=gen).half()
+    nhwc = lambda t: t.permute(0, 2, 3, 1).contiguous()
+    conv, gn, att = [], [], []
+    wp = ops.conv_weight_pack(w_c.to(dev))
+    for n_strips in (2, 4, 8):
+        i = n_strips // 2
+        # conv: this rank's strip, stale halo rows from its neighbours
+        hs = 64 // n_strips
+        xs = nhwc(x_c)[:, i * hs:(i + 1) * hs]
+        nset = sets(2 * (xs.numel() + w_c.numel() + 2 * hs * 64 * 640))
+        X = [xs.to(dev) for _ in range(nset)]
+        W = [wp.clone() for _ in range(nset)]
+        top = nhwc(x_c)[:, i * hs - 1:i * hs].to(dev)
+        bot = nhwc(x_c)[:, (i + 1) * hs:(i + 1) * hs + 1].to(dev) if (i + 1) * hs < 64 else None  # last strip: image edge
+        Y = [torch.empty(2, hs, 64, 640, device=dev, dtype=torch.float16) for _ in range(nset)]
+        bd = b_c.to(dev)
+        us = _chain_us(lambda k: ops.conv3x3(X[k], W[k], bd, top=top, bot=bot, out=Y[k]), nset)
+        fl = 2.0 * 9 * 640 * 640 * 2 * hs * 64
+        xf, wf, bf = x_c.float(), w_c.float(), b_c.float()
+        strips = torch.chunk(xf, n_strips, 2)
+        stale = [po.conv2d_boundary(t, 1) for t in strips]
+        cpu_s = _cpu_seconds(lambda: po.conv2d_pp(strips[i], wf, bf, 1, 1, stale, i, n_strips))
+        conv.append({"strips": n_strips, "strip_shape": [2, 640, hs, 64], "us": round(us, 2), "tflops": round(fl / us / 1e6, 1),
+                     "frac_of_burst_peak": round(fl / us / 1e6 / peaks["tflops_burst"], 3), "cpu_s": round(cpu_s, 4)})
+        del X, W, Y
+        # GroupNorm + SiLU, stale moments, one launch
+        hg = 32 // n_strips
+        xg = nhwc(x_g)[:, i * hg:(i + 1) * hg].contiguous()
+        nset = sets(4 * xg.numel())
+        Xg = [xg.to(dev) for _ in range(nset)]
+        Yg = [torch.empty_like(Xg[0]) for _ in range(nset)]
+        gstrips = torch.chunk(x_g.float(), n_strips, 2)
+        mom = [po.groupnorm_moments(t, 32) for t in gstrips]
+        peers = [m.reshape(2, 2, 32).float().contiguous().to(dev) for m in mom]
+        gad, bed = ga.to(dev), be.to(dev)
+        us = _chain_us(lambda k: ops.groupnorm_fused(Xg[k], 32, 1e-5, gad, bed, peers, i, ops.MODE_STALE, silu=True, out=Yg[k]), nset)
+        nbytes = 2.0 * xg.numel() * 2
+        cpu_s = _cpu_seconds(lambda: torch.nn.functional.silu(po.groupnorm_pp(gstrips[i], 32, 1e-5, ga.float(), be.float(), mom, i, "stale")))
+        gn.append({"strips": n_strips, "strip_shape": [2, 1280, hg, 32], "us": round(us, 2), "gbps": round(nbytes / us / 1e3, 1),
+                   "frac_of_hbm_peak": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4), "algorithmic_bytes": nbytes, "cpu_s": round(cpu_s, 5)})
+        del Xg, Yg
+        # self-attention core: this strip's queries against all strips' K/V slots
+        ls = 4096 // n_strips
+        qs = q_a[:, i * ls:(i + 1) * ls].contiguous()
+        nset = sets(2 * (qs.numel() * 2 + kv_a.numel()))
+        Q = [qs.to(dev) for _ in range(nset)]
+        KV = [[kv_a[:, j * ls:(j + 1) * ls].contiguous().to(dev) for j in range(n_strips)] for _ in range(nset)]
+        O = [torch.empty_like(Q[0]) for _ in range(nset)]
+        us = _chain_us(lambda k: ops.attention(Q[k], KV[k], 10, out=O[k]), nset)
+        fl = 4.0 * 2 * 10 * ls * 4096 * 64
+        qf, kvf = qs.float(), kv_a.float()
+        cpu_s = _cpu_seconds(lambda: po._sdpa_heads(qf, kvf, 10))
+        att.append({"strips": n_strips, "queries": ls, "keys": 4096, "us": round(us, 2), "tflops": round(fl / us / 1e6, 1),
+                    "frac_of_burst_peak": round(fl / us / 1e6 / peaks["tflops_burst"], 3), "cpu_s": round(cpu_s, 4)})
+        del Q, KV, O
+    _lib.device_status()
+    out["conv3x3_2x640x64x64"], out["groupnorm_silu_2x1280x32x32"], out["self_attention_2x4096x640_h10"] = conv, gn, att
+    print(json.dumps(out), flush=True)
+
+
 # --------------------------------------------------------------------------- main arm
 def workload_name(args) -> str:
     return (f"SDXL {args.height}x{args.width} UNet loop: latent 1x4x{args.height // 8}x{args.width // 8}, CFG batch 2, guidance 5.0, "
@@ -484,10 +639,15 @@ def main():
     ap.add_argument("--width", type=int, default=1024)
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the cpu_baseline leg")
+    ap.add_argument("--workload", default="loop", choices=["loop", "ops"],
+                    help="loop: the denoising loop (the benchmark line); ops: the isolated matmul / conv / GroupNorm / attention configurations")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
     args.warmup_reference = args.warmup
+    if args.workload == "ops":
+        run_ops_workload(args)
+        return
     if args.impl == "reference":
         if args.steps is None:
             args.steps = 10  # default run: ten full-size CPU forwards, a couple of minutes
