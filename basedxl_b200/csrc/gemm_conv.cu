@@ -5,10 +5,13 @@
 //     tiles are gathered by TMA row by row from three sources: the fresh local
 //     strip and the (stale) boundary rows of the strips above and below.
 //
-// Roles inside a CTA of 224 threads (one CTA per SM, tiles strided by grid):
-//   warps 0, 6  TMA producers (A and B operand): fill a ring of {A 128x64, B BNx64} fp16 stages
-//   warp 1      allocates tensor memory and issues tcgen05.mma (one lane)
-//   warps 2..5  epilogue: tcgen05.ld the fp32 accumulator, add bias/residual,
+// Roles inside a CTA of 352 threads (one CTA per SM, tiles strided by grid):
+//   warps 8, 10 TMA producers (A and B operand): fill a ring of {A 128x64, B BNx64} fp16 stages
+//   warp 9      allocates tensor memory and issues tcgen05.mma (one lane)
+//   warps 0..7  epilogue, two warps per 32-row quarter of the tile (warps q and q + 4 share the
+//               tensor-memory lanes of quarter q and take the even / odd 32-column chunks: one
+//               epilogue warp per scheduler is bound by its own instruction latencies, two
+//               interleave): tcgen05.ld the fp32 accumulator, add bias/residual,
 //               convert and store; runs while the next tile's mainloop fills the
 //               other accumulator buffer (two TMEM buffers of BN columns).  Nothing
 //               the epilogue needs from global memory is fetched on its critical
@@ -42,7 +45,9 @@ namespace bxl {
 constexpr int kBM = 128;           // tile rows (= TMEM lanes, UMMA M)
 constexpr int kBK = 64;            // K per stage: 64 fp16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;         // K of one tcgen05.mma.kind::f16
-constexpr int kGemmThreads = 224;   // warp 0: A loads, warp 1: MMA, warps 2..5: epilogue, warp 6: B loads
+constexpr int kGemmThreads = 352;   // warps 0..7: epilogue, warp 8: A loads, warp 9: MMA, warp 10: B loads
+constexpr int kEpiThreads = 256;
+constexpr int kWarpA = 8, kWarpMma = 9, kWarpB = 10;
 constexpr int kMaxSeg = 3;
 constexpr int kABytes = kBM * kBK * 2;       // 16 KB
 constexpr int kSmemBudget = 227 * 1024;      // dynamic shared memory available to one CTA
@@ -238,13 +243,16 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, float (&f)[32],
   }
 }
 
-template <bool kConv, bool kPair>
+// kSplit: the K loop is split over the CTAs of a cluster (p.split of them); a separate
+// instantiation, so that each variant carries only its own epilogue (and its registers).
+template <bool kConv, bool kPair, bool kSplit>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid_constant__ GemmParams p) {
+  static_assert(!(kPair && kSplit), "a CTA pair walks the whole K range");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const int BN = p.bn;
-  const int S = kPair ? 1 : p.split;
+  const int S = kSplit ? p.split : 1;
   const int b_rows = kPair ? BN / 2 : BN;       // rows of the B tile this CTA stages
   const int stage_bytes = kABytes + b_rows * 128;
   constexpr int kWidth = kPair ? 2 : 1;          // CTAs that cooperate on one tile (besides a K split)
@@ -277,15 +285,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4 * kWidth);  // one arrival per epilogue warp (of both CTAs in pair mode)
+      mbar_init(tempty_bar(a), 8 * kWidth);  // one arrival per epilogue warp (of both CTAs in pair mode)
     }
-    const uint32_t peers_threads = (S > 1) ? (S - 1) * 128u : 1u;  // every epilogue thread of every peer
+    const uint32_t peers_threads = (S > 1) ? (S - 1) * static_cast<uint32_t>(kEpiThreads) : 1u;  // every epilogue thread of every peer
     mbar_init(recv_full_bar, peers_threads);
     mbar_init(recv_free_bar, peers_threads);
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 1) {
+  if (warp == kWarpMma) {
     if (kPair) {
       tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), tmem_cols);
       tmem_relinquish_pair();
@@ -302,7 +310,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
   // Everything above overlaps the previous kernel's tail; global data from here on.  With static
   // weights the B producer does not wait: it fills the ring with B tiles while the previous
   // kernel finishes (A, written by that kernel, is only loaded after the wait).
-  if (!(p.b_static && warp == 6)) pdl_wait();
+  if (!(p.b_static && warp == kWarpB)) pdl_wait();
 
   // ---- tile enumeration ------------------------------------------------------
   const int tiles_n = (p.N + BN - 1) / BN;
@@ -320,12 +328,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
   const int first_tile = blockIdx.x / (S * kWidth);
   const int tile_step = gridDim.x / (S * kWidth);
 
-  if (warp == 0 || warp == 6) {
+  if (warp == kWarpA || warp == kWarpB) {
     // ======================= TMA producers =======================
     // Issuing a tiled copy occupies the issuing thread for a few hundred cycles, so the A
     // and B operands are fed by two threads in different warps; both arrive on the stage's
     // "full" barrier with the bytes they ordered.
-    const bool loads_a = (warp == 0);
+    const bool loads_a = (warp == kWarpA);
     if (lane == 0) {
       for (int s = 0; s < kMaxSeg; ++s) tma_prefetch_desc(loads_a ? &p.a_map[s] : &p.b_map[s]);
       if (loads_a && kConv) tma_prefetch_desc(&p.a_rows_map);
@@ -432,7 +440,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == kWarpMma) {
     // ======================= MMA issuer =======================
     if (kPair && crank != 0) {
       // odd CTA of a pair: the leader issues the MMAs for both
@@ -500,8 +508,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
       }
     }
   } else {
-    // ======================= epilogue (warps 2..5) =======================
+    // ======================= epilogue (warps 0..7) =======================
     const int quarter = warp & 3;  // TMEM lane quarter this warp may access
+    const int half = warp >> 2;    // which of the quarter's two warps: it takes the chunks c with (c & 1) == half
     const int row_in_tile = quarter * 32 + lane;
     const int chunks = BN / 32;
     const int cps = chunks / S;    // 32-column chunks per owner slice
@@ -531,9 +540,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
       const bool has_ln = !kConv && (p.ln_part != nullptr);
       const bool has_bias = (p.bias != nullptr) || (p.bias_f32 != nullptr) || (kConv && p.bias_rows != nullptr);
       if (has_bias || has_ln) {
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        const int et = (warp - 2) * 32 + lane;   // 0..127
-        for (int j = et; j < BN; j += 128) {
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const int et = warp * 32 + lane;   // 0..255
+        for (int j = et; j < BN; j += kEpiThreads) {
           float b = 0.f, cs = 0.f;
           if (n0 + j < p.N) {
             if (p.bias_f32) b += p.bias_f32[n0 + j];
@@ -544,7 +553,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
           s_bias[j] = b;
           if (has_ln) s_colsum[j] = cs;
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, 256;" ::: "memory");
       }
       // LayerNorm fold: this row's mean and reciprocal standard deviation from the partial sums
       // the producer of A left (read while this tile's MMAs still run)
@@ -562,21 +571,27 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
         ln.b = -ln.a * mean;
       }
       RowStat stat{0.f, 0.f};
-      ResidualChunk res_cur, res_next, res_next2;
-      res_cur.valid = res_next.valid = res_next2.valid = false;
-      if (S == 1) {
-        // the residual of the first two chunks travels while the MMAs of this tile still run
-        load_residual(p, out_row, n0, res_cur);
-        if (BN > 32) load_residual(p, out_row, n0 + 32, res_next);
+      // This warp's chunks are c = half, half + 2, ... ; the residual of a chunk is fetched while
+      // the chunk before it (of this warp) is converted and stored.
+      ResidualChunk res_cur, res_next;
+      res_cur.valid = res_next.valid = false;
+      if (!kSplit) {
+        // the residual of the first chunk travels while the MMAs of this tile still run
+        if (half < chunks) load_residual(p, out_row, n0 + half * 32, res_cur);
       }
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.dev_status, 300)) break;
       __syncwarp();
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-      if (S == 1) {
-        // two chunks per trip: the accumulator load of the second is in flight while the first is
-        // converted and stored, and the residual is fetched two chunks ahead
-        auto emit = [&](const uint32_t (&v)[32], int c) {
+      if constexpr (!kSplit) {
+        // One chunk at a time per warp (measured: several accumulator loads in flight per warp do not
+        // shorten the epilogue; a second warp on the same scheduler does).
+#pragma unroll 1
+        for (int c = half; c < chunks; c += 2) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_row + c * 32, v);
+          if (c + 2 < chunks) load_residual(p, out_row, n0 + (c + 2) * 32, res_next);
+          tmem_ld_wait();
           const int nb = n0 + c * 32;
           if (out_row >= 0 && nb < p.N) {
             float f[32];
@@ -586,23 +601,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
                                has_ln ? s_colsum + c * 32 : nullptr, ln, stat);
           }
           res_cur = res_next;
-          res_next = res_next2;
-          res_next2.valid = false;
-        };
-        uint32_t va[32], vb[32];
-        tmem_ld_32x32(t_row, va);
-#pragma unroll 1
-        for (int c = 0; c < chunks; c += 2) {
-          if (c + 2 < chunks) load_residual(p, out_row, n0 + (c + 2) * 32, res_next2);
-          tmem_ld_wait();
-          if (c + 1 < chunks) tmem_ld_32x32(t_row + (c + 1) * 32, vb);
-          emit(va, c);
-          if (c + 1 < chunks) {
-            if (c + 3 < chunks) load_residual(p, out_row, n0 + (c + 3) * 32, res_next2);
-            tmem_ld_wait();
-            if (c + 2 < chunks) tmem_ld_32x32(t_row + (c + 2) * 32, va);
-            emit(vb, c + 1);
-          }
+          res_next.valid = false;
         }
       } else {
         // ---- split-K: push the partial sums of the peers' column slices into their
@@ -610,37 +609,46 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
         // peers must have finished reading what was pushed for the previous tile
         if (it > 0 && !mbar_wait_cluster(recv_free_bar, (it - 1) & 1u, abort_flag, p.dev_status, 301)) break;
         __syncwarp();
+        {
+          const int own_lo = static_cast<int>(crank) * cps;
+          const int nf = chunks - cps;                                  // chunks owned by the peers
 #pragma unroll 1
-        for (int c = 0; c < chunks; ++c) {
-          const uint32_t owner = c / cps;
-          if (owner == crank) continue;
-          uint32_t v[32];
-          tmem_ld_32x32(t_row + c * 32, v);
-          tmem_ld_wait();
-          const uint32_t slot = (crank < owner) ? crank : crank - 1;   // this CTA's slot at the owner
-          const uint32_t base = recv_base + ((slot * cps + (c % cps)) * 8u * kBM + row_in_tile) * 16u;
-          const uint32_t remote = map_to_cta(base, owner);
+          for (int fi = half; fi < nf; fi += 2) {
+            const int c = fi < own_lo ? fi : fi + cps;                   // fi-th chunk that is not this CTA's own
+            uint32_t v[32];
+            tmem_ld_32x32(t_row + c * 32, v);
+            tmem_ld_wait();
+            const uint32_t owner = c / cps;
+            const uint32_t slot = (crank < owner) ? crank : crank - 1;   // this CTA's slot at the owner
+            const uint32_t base = recv_base + ((slot * cps + (c % cps)) * 8u * kBM + row_in_tile) * 16u;
+            const uint32_t remote = map_to_cta(base, owner);
 #pragma unroll
-          for (int q = 0; q < 8; ++q)
-            st_cluster_f32x4(remote + q * kBM * 16u, __uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
-                             __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+            for (int q = 0; q < 8; ++q)
+              st_cluster_f32x4(remote + q * kBM * 16u, __uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                               __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+          }
         }
         for (uint32_t o = 0; o < static_cast<uint32_t>(S); ++o)
           if (o != crank) mbar_arrive_remote(map_to_cta(recv_full_bar, o));
-        // own slice: wait for every peer's partials (the first chunk's residual travels meanwhile)
-        load_residual(p, out_row, n0 + static_cast<int>(crank) * cps * 32, res_cur);
+        // own slice (this warp's chunks of it): wait for every peer's partials; the first chunk's
+        // residual and accumulator load travel meanwhile
+        const bool has_own = half < cps;
+        uint32_t v[32];
+        if (has_own) {
+          load_residual(p, out_row, n0 + (static_cast<int>(crank) * cps + half) * 32, res_cur);
+          tmem_ld_32x32(t_row + (static_cast<int>(crank) * cps + half) * 32, v);
+        }
         if (!mbar_wait_cluster(recv_full_bar, it & 1u, abort_flag, p.dev_status, 302)) break;
         __syncwarp();
 #pragma unroll 1
-        for (int cc = 0; cc < cps; ++cc) {
+        for (int cc = half; cc < cps; cc += 2) {
           const int c = crank * cps + cc;
-          uint32_t v[32];
-          tmem_ld_32x32(t_row + c * 32, v);
-          if (cc + 1 < cps) load_residual(p, out_row, n0 + (c + 1) * 32, res_next);
+          if (cc + 2 < cps) load_residual(p, out_row, n0 + (c + 2) * 32, res_next);
           tmem_ld_wait();
           float f[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          if (cc + 2 < cps) tmem_ld_32x32(t_row + (c + 2) * 32, v);   // this warp's next own chunk, in flight during the reduction
           for (int slot = 0; slot < S - 1; ++slot) {
             const uint8_t* src = smem_gen + (recv_base - smem_base) + ((slot * cps + cc) * 8 * kBM + row_in_tile) * 16;
 #pragma unroll
@@ -661,7 +669,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
           if (o != crank) mbar_arrive_remote(map_to_cta(recv_free_bar, o));
       }
       if (!kConv && p.stat_out && out_row >= 0)
-        p.stat_out[out_row * p.stat_parts + tn * S + (S > 1 ? static_cast<int>(crank) : 0)] = make_float2(stat.s, stat.q);
+        p.stat_out[out_row * p.stat_parts + (tn * S + (S > 1 ? static_cast<int>(crank) : 0)) * 2 + half] = make_float2(stat.s, stat.q);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
@@ -683,7 +691,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
   }
   // no CTA of a cluster may leave while a peer can still write into its shared memory
   if (S > 1 || kPair) cluster_sync_all();
-  if (warp == 1) {
+  if (warp == kWarpMma) {
     __syncwarp();
     tc_fence_after_sync();
     if (kPair) tmem_dealloc_pair(tmem_base, tmem_cols);
@@ -754,33 +762,34 @@ static TileConfig choose_tiles(int tiles_m, int N, int num_kb, bool b_kn, int fo
   return best;
 }
 
-template <bool kConv, bool kPair>
+template <bool kConv, bool kPair, bool kSplit>
 static int launch_one(const GemmParams& p, int num_units, cudaStream_t stream) {
   const int b_rows = kPair ? p.bn / 2 : p.bn;
-  const int smem = p.stages * (kABytes + b_rows * 128) + recv_bytes(p.bn, kPair ? 1 : p.split) + kSmemMisc +
+  const int smem = p.stages * (kABytes + b_rows * 128) + recv_bytes(p.bn, kSplit ? p.split : 1) + kSmemMisc +
                    (p.ln_part ? kSmemLnExtra : 0);
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    if (int rc = check_cuda(cudaFuncSetAttribute(gemm_conv_kernel<kConv, kPair>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget),
+    if (int rc = check_cuda(cudaFuncSetAttribute(gemm_conv_kernel<kConv, kPair, kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget),
                             "cudaFuncSetAttribute(gemm)"))
       return rc;
     configured[dev] = true;
   }
-  const int width = kPair ? 2 : p.split;
+  const int width = kPair ? 2 : (kSplit ? p.split : 1);
   int clusters = sm_count() / width;
   if (clusters > num_units) clusters = num_units;
   if (clusters < 1) clusters = 1;
-  return launch_kernel("gemm_conv_kernel launch", gemm_conv_kernel<kConv, kPair>, dim3(clusters * width), dim3(kGemmThreads), smem,
+  return launch_kernel("gemm_conv_kernel launch", gemm_conv_kernel<kConv, kPair, kSplit>, dim3(clusters * width), dim3(kGemmThreads), smem,
                        stream, width, p);
 }
 
 // tiles_m: 128-row tiles along M; tiles_n: tiles along N
 template <bool kConv>
 static int launch(const GemmParams& p, int tiles_m, int tiles_n, cudaStream_t stream) {
-  if (p.pair) return launch_one<kConv, true>(p, ((tiles_m + 1) / 2) * tiles_n, stream);
-  return launch_one<kConv, false>(p, tiles_m * tiles_n, stream);
+  if (p.pair) return launch_one<kConv, true, false>(p, ((tiles_m + 1) / 2) * tiles_n, stream);
+  if (p.split > 1) return launch_one<kConv, false, true>(p, tiles_m * tiles_n, stream);
+  return launch_one<kConv, false, false>(p, tiles_m * tiles_n, stream);
 }
 
 static int aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -953,7 +962,7 @@ extern "C" int bxl_gemm_fused_f16(const bxl_gemm_fused_args* a, int* row_stats_p
                                      g_force_pair < 0 ? kDefaultPair : g_force_pair, 0.0, ln ? kSmemLnExtra : 0);
   const int tiles_n = (N + tc.bn - 1) / tc.bn;
   if (a->row_stats) {
-    const long long parts = (long long)tiles_n * (tc.pair ? 1 : tc.split);
+    const long long parts = 2ll * tiles_n * (tc.pair ? 1 : tc.split);  // two epilogue warps per row and column slice
     if (a->row_stats_capacity < 2ll * M * parts)
       return fail(kErrTooLarge, "bxl_gemm_fused_f16: row statistics need %lld floats, %lld given", 2ll * M * parts, a->row_stats_capacity);
     *row_stats_parts = (int)parts;

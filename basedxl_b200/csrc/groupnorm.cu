@@ -256,7 +256,7 @@ __global__ void __launch_bounds__(512) groupnorm_fused_kernel(const GnFusedParam
   float* s_stat = s_xch + kGnfMaxCluster * kGnfMaxGroupsPerBlock * 2;      // [gb][2] mean, rstd; then stale terms [gb][4]
   float* s_ab = s_stat + kGnfMaxGroupsPerBlock * 6;                        // [2][cb]
   float* s_part = s_ab + 2 * cb;                                           // [rows][2][cb]
-  uint4* s_slab = reinterpret_cast<uint4*>(s_part + (size_t)rows * 2 * cb);  // [p1 - p0][bv] when kept
+  uint4* s_slab = reinterpret_cast<uint4*>(s_part + (size_t)rows * 2 * cb + 2 * kGnfMaxGroupsPerBlock * 16);  // after the per-warp sums; [p1 - p0][bv] when kept
   const int v = threadIdx.x % bv, r = threadIdx.x / bv;
   const int g0 = cblk * gb;                               // first group of this block
   pdl_wait();
@@ -302,25 +302,36 @@ __global__ void __launch_bounds__(512) groupnorm_fused_kernel(const GnFusedParam
     *reinterpret_cast<float4*>(d2 + 4) = make_float4(s2[4], s2[5], s2[6], s2[7]);
   }
   __syncthreads();
-  // ---- this CTA's per-group sums, in a fixed order, sent to every CTA of the cluster
+  // ---- this CTA's per-group sums, in a fixed order, sent to every CTA of the cluster.  Every warp
+  //      folds its share of the pixel rows for every (group, moment); the per-warp results are then
+  //      added in warp order: the summation order is fixed, whatever the scheduling.
   {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;  // whole warps only
+    float* s_red = s_part + (size_t)rows * 2 * cb;   // [2 * gb][warps]; lives behind the per-thread partials (see the host's sizing)
     if (warp < warps) {
-      for (int i = warp; i < 2 * gb; i += warps) {
+      const int rpw = (rows + warps - 1) / warps;    // pixel rows per warp
+      const int r_lo = min(rows, warp * rpw), r_hi = min(rows, r_lo + rpw);
+      for (int i = 0; i < 2 * gb; ++i) {
         const int g = i >> 1, which = i & 1;
         float acc = 0.f;
-        for (int e = lane; e < rows * cpg; e += 32) {
-          const int rr = e / cpg, c = e - rr * cpg;
+        for (int e = lane; e < (r_hi - r_lo) * cpg; e += 32) {
+          const int rr = r_lo + e / cpg, c = e % cpg;
           acc += s_part[((size_t)rr * 2 + which) * cb + g * cpg + c];
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (lane < p.cs) {
-          const uint32_t dst = smem_u32(&s_xch[((int)crank * kGnfMaxGroupsPerBlock + g) * 2 + which]);
-          if (p.cs > 1) st_cluster_f32(map_to_cta(dst, (uint32_t)lane), acc);
-          else s_xch[(g) * 2 + which] = acc;
-        }
+        if (lane == 0) s_red[i * warps + warp] = acc;
       }
+    }
+    __syncthreads();
+    if (threadIdx.x < 2 * gb * p.cs) {
+      const int i = threadIdx.x % (2 * gb), dst_cta = threadIdx.x / (2 * gb);
+      float acc = 0.f;
+      for (int w = 0; w < warps; ++w) acc += s_red[i * warps + w];
+      const int g = i >> 1, which = i & 1;
+      const uint32_t dst = smem_u32(&s_xch[((int)crank * kGnfMaxGroupsPerBlock + g) * 2 + which]);
+      if (p.cs > 1) st_cluster_f32(map_to_cta(dst, (uint32_t)dst_cta), acc);
+      else s_xch[g * 2 + which] = acc;
     }
   }
   if (p.cs > 1) cluster_sync_all();
@@ -496,16 +507,24 @@ extern "C" int bxl_groupnorm_fused_f16(const void* x, void* y, long long img_str
     for (int j = 0; j < n_peers; ++j)
       if (!p.peers.ptr[j]) return fail(kErrInvalidArg, "bxl_groupnorm_fused_f16: peer %d null", j);
   const int nblk = C / cb, bv = cb / 8;
-  // pixel ranges per cluster: enough CTAs to fill the machine, slabs small enough to keep on chip
+  // pixel ranges per cluster: one CTA per SM or a little more (every further CTA costs a cluster
+  // exchange and idles threads), slabs small enough to keep on chip
   int cs = 1;
-  while (cs < kGnfMaxCluster && ((long long)B * nblk * cs < 2ll * sm_count() && (long long)HW * cb * 2 / cs > 8192)) cs *= 2;
+  while (cs < kGnfMaxCluster && (long long)B * nblk * cs < sm_count() && HW / (cs * 2) >= 32) cs *= 2;
   while (cs < kGnfMaxCluster && (long long)HW * cb * 2 / cs > 160 * 1024) cs *= 2;
   const int per = (HW + cs - 1) / cs;
   const long long slab = (long long)per * cb * 2;
-  int threads = 512;
-  auto fixed_smem = [&](int th) { return (size_t)(kGnfMaxCluster * kGnfMaxGroupsPerBlock * 2 + kGnfMaxGroupsPerBlock * 6 + 2 * cb) * 4 + (size_t)(th / bv) * 2 * cb * 4; };
-  if (slab + (long long)fixed_smem(512) > 200 * 1024 && slab + (long long)fixed_smem(256) <= 200 * 1024) threads = 256;
-  threads = (threads / bv) * bv;
+  // threads: one pixel row per thread row, at most 512 threads, whole warps, a whole number of pixel rows
+  auto fixed_smem = [&](int th) {
+    return (size_t)(kGnfMaxCluster * kGnfMaxGroupsPerBlock * 2 + kGnfMaxGroupsPerBlock * 6 + 2 * cb) * 4 + (size_t)(th / bv) * 2 * cb * 4 +
+           (size_t)2 * kGnfMaxGroupsPerBlock * 16 * 4;
+  };
+  int rows_t = per < 512 / bv ? per : 512 / bv;
+  if (slab + (long long)fixed_smem(rows_t * bv) > 200 * 1024 && rows_t > 256 / bv) rows_t = 256 / bv;
+  if (rows_t < 1) rows_t = 1;
+  // whole warps (the reductions run on whole warps) and enough threads for the cluster exchange
+  int threads = ((rows_t * bv + 31) / 32) * 32;
+  if (threads < 128) threads = 128;
   const int keep = slab + (long long)fixed_smem(threads) <= 200 * 1024;
   const size_t smem = fixed_smem(threads) + (keep ? (size_t)slab : 0) + 16;
   static bool configured[64] = {};

@@ -4,7 +4,8 @@ flushed between launches) and print one JSON line with its achieved rate.
     python -m basedxl_b200.kernel_bench gemm --M 2048 --K 1280 --N 10240
     python -m basedxl_b200.kernel_bench conv --B 2 --Cin 640 --Cout 640 --H 64 --W 64
     python -m basedxl_b200.kernel_bench attention --B 2 --heads 10 --Lq 4096 --Lslot 4096 --slots 1
-    python -m basedxl_b200.kernel_bench groupnorm --B 2 --C 1280 --H 32 --W 32
+    python -m basedxl_b200.kernel_bench groupnorm --B 2 --C 1280 --H 32 --W 32          # two-launch form
+    python -m basedxl_b200.kernel_bench groupnorm_fused --B 2 --C 1280 --H 32 --W 32    # one-launch form
 
 The same command line is what the profiler captures are taken on (few launches,
 small device footprint).
@@ -41,7 +42,7 @@ def _time(fn, iters: int, warmup: int, flush: bool = True) -> float:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "conv", "attention", "groupnorm", "geglu", "layernorm"])
+    ap.add_argument("kernel", choices=["gemm", "conv", "attention", "groupnorm", "groupnorm_fused", "geglu", "layernorm"])
     for n, d in [("M", 2048), ("K", 1280), ("N", 1280), ("B", 2), ("Cin", 640), ("Cout", 640), ("C", 1280), ("H", 64), ("W", 64),
                  ("heads", 10), ("Lq", 4096), ("Lslot", 4096), ("slots", 1), ("stride", 1), ("iters", 10), ("warmup", 3),
                  ("bn", 0), ("split", 0), ("pair", -1)]:
@@ -84,6 +85,13 @@ def main():
             ops.groupnorm_apply(x, 32, 1e-5, gamma, beta, m, silu=True, out=y)
 
         work, unit, desc = 2.0 * x.numel() * 2, "GB/s", {"B": a.B, "C": a.C, "H": a.H, "W": a.W, "launches": 2}
+    elif a.kernel == "groupnorm_fused":
+        x = rn(a.B, a.H, a.W, a.C)
+        gamma, beta = rn(a.C), rn(a.C)
+        y = torch.empty_like(x)
+        mom = torch.empty(2, a.B, 32, device=dev, dtype=torch.float32)
+        fn = lambda: ops.groupnorm_fused(x, 32, 1e-5, gamma, beta, silu=True, fresh_out=mom, out=y)
+        work, unit, desc = 2.0 * x.numel() * 2, "GB/s", {"B": a.B, "C": a.C, "H": a.H, "W": a.W, "launches": 1}
     elif a.kernel == "geglu":
         h = rn(a.M, 2 * a.N)
         fn = lambda: ops.geglu(h)

@@ -100,7 +100,7 @@ int bxl_gemm_geglu_f16(const void* A, long long lda, const void* B, long long ld
  *   - row statistics out: with `row_stats` set, every CTA also writes, per output row, the sum and
  *     the sum of squares of the fp16 values it stored for the column slice it owns:
  *     row_stats[m][part][2] fp32, `*row_stats_parts` partials per row (the count follows from
- *     the tiling chosen for the problem and is at most N/32; row_stats_capacity = floats available);
+ *     the tiling chosen for the problem and is at most N/16; row_stats_capacity = floats available);
  *   - LayerNorm folded in: with `ln_partials` set (such partials of the rows of A, `ln_parts` per
  *     row), A is taken as the UN-normalised input of a LayerNorm over K, B as the weight with the
  *     LayerNorm gain multiplied into its columns, `ln_colsum[n]` = sum_k B[n,k] (fp32), and the
