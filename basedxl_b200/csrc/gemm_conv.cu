@@ -5,11 +5,11 @@
 //     tiles are gathered by TMA row by row from three sources: the fresh local
 //     strip and the (stale) boundary rows of the strips above and below.
 //
-// Roles inside a CTA of 352 threads (one CTA per SM, tiles strided by grid):
+// Roles inside a CTA of 352 threads (one CTA per SM, tiles strided by grid; kEpiSub = 2):
 //   warps 8, 10 TMA producers (A and B operand): fill a ring of {A 128x64, B BNx64} fp16 stages
 //   warp 9      allocates tensor memory and issues tcgen05.mma (one lane)
-//   warps 0..7  epilogue, two warps per 32-row quarter of the tile (warps q and q + 4 share the
-//               tensor-memory lanes of quarter q and take the even / odd 32-column chunks: one
+//   warps 0..7  epilogue, kEpiSub warps per 32-row quarter of the tile (warps q, q + 4, ... share the
+//               tensor-memory lanes of quarter q and take every kEpiSub-th 32-column chunk: one
 //               epilogue warp per scheduler is bound by its own instruction latencies, two
 //               interleave): tcgen05.ld the fp32 accumulator, add bias/residual,
 //               convert and store; runs while the next tile's mainloop fills the
@@ -45,9 +45,13 @@ namespace bxl {
 constexpr int kBM = 128;           // tile rows (= TMEM lanes, UMMA M)
 constexpr int kBK = 64;            // K per stage: 64 fp16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;         // K of one tcgen05.mma.kind::f16
-constexpr int kGemmThreads = 352;   // warps 0..7: epilogue, warp 8: A loads, warp 9: MMA, warp 10: B loads
-constexpr int kEpiThreads = 256;
-constexpr int kWarpA = 8, kWarpMma = 9, kWarpB = 10;
+#ifndef BXL_EPI_SUB
+#define BXL_EPI_SUB 2
+#endif
+constexpr int kEpiSub = BXL_EPI_SUB;            // epilogue warps per 32-row quarter of the tile
+constexpr int kEpiThreads = kEpiSub * 128;
+constexpr int kWarpA = 4 * kEpiSub, kWarpMma = kWarpA + 1, kWarpB = kWarpA + 2;   // after the epilogue warps: A loads, MMA, B loads
+constexpr int kGemmThreads = (4 * kEpiSub + 3) * 32;
 constexpr int kMaxSeg = 3;
 constexpr int kABytes = kBM * kBK * 2;       // 16 KB
 constexpr int kSmemBudget = 227 * 1024;      // dynamic shared memory available to one CTA
@@ -285,7 +289,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 8 * kWidth);  // one arrival per epilogue warp (of both CTAs in pair mode)
+      mbar_init(tempty_bar(a), 4 * kEpiSub * kWidth);  // one arrival per epilogue warp (of both CTAs in pair mode)
     }
     const uint32_t peers_threads = (S > 1) ? (S - 1) * static_cast<uint32_t>(kEpiThreads) : 1u;  // every epilogue thread of every peer
     mbar_init(recv_full_bar, peers_threads);
@@ -510,7 +514,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
   } else {
     // ======================= epilogue (warps 0..7) =======================
     const int quarter = warp & 3;  // TMEM lane quarter this warp may access
-    const int half = warp >> 2;    // which of the quarter's two warps: it takes the chunks c with (c & 1) == half
+    const int half = warp >> 2;    // which of the quarter's kEpiSub warps: it takes the chunks c with c % kEpiSub == half
     const int row_in_tile = quarter * 32 + lane;
     const int chunks = BN / 32;
     const int cps = chunks / S;    // 32-column chunks per owner slice
@@ -540,8 +544,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
       const bool has_ln = !kConv && (p.ln_part != nullptr);
       const bool has_bias = (p.bias != nullptr) || (p.bias_f32 != nullptr) || (kConv && p.bias_rows != nullptr);
       if (has_bias || has_ln) {
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        const int et = warp * 32 + lane;   // 0..255
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        const int et = warp * 32 + lane;   // 0..kEpiThreads-1
         for (int j = et; j < BN; j += kEpiThreads) {
           float b = 0.f, cs = 0.f;
           if (n0 + j < p.N) {
@@ -553,7 +557,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
           s_bias[j] = b;
           if (has_ln) s_colsum[j] = cs;
         }
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
       }
       // LayerNorm fold: this row's mean and reciprocal standard deviation from the partial sums
       // the producer of A left (read while this tile's MMAs still run)
@@ -587,10 +591,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
         // One chunk at a time per warp (measured: several accumulator loads in flight per warp do not
         // shorten the epilogue; a second warp on the same scheduler does).
 #pragma unroll 1
-        for (int c = half; c < chunks; c += 2) {
+        for (int c = half; c < chunks; c += kEpiSub) {
           uint32_t v[32];
           tmem_ld_32x32(t_row + c * 32, v);
-          if (c + 2 < chunks) load_residual(p, out_row, n0 + (c + 2) * 32, res_next);
+          if (c + kEpiSub < chunks) load_residual(p, out_row, n0 + (c + kEpiSub) * 32, res_next);
           tmem_ld_wait();
           const int nb = n0 + c * 32;
           if (out_row >= 0 && nb < p.N) {
@@ -613,7 +617,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
           const int own_lo = static_cast<int>(crank) * cps;
           const int nf = chunks - cps;                                  // chunks owned by the peers
 #pragma unroll 1
-          for (int fi = half; fi < nf; fi += 2) {
+          for (int fi = half; fi < nf; fi += kEpiSub) {
             const int c = fi < own_lo ? fi : fi + cps;                   // fi-th chunk that is not this CTA's own
             uint32_t v[32];
             tmem_ld_32x32(t_row + c * 32, v);
@@ -641,14 +645,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
         if (!mbar_wait_cluster(recv_full_bar, it & 1u, abort_flag, p.dev_status, 302)) break;
         __syncwarp();
 #pragma unroll 1
-        for (int cc = half; cc < cps; cc += 2) {
+        for (int cc = half; cc < cps; cc += kEpiSub) {
           const int c = crank * cps + cc;
-          if (cc + 2 < cps) load_residual(p, out_row, n0 + (c + 2) * 32, res_next);
+          if (cc + kEpiSub < cps) load_residual(p, out_row, n0 + (c + kEpiSub) * 32, res_next);
           tmem_ld_wait();
           float f[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-          if (cc + 2 < cps) tmem_ld_32x32(t_row + (c + 2) * 32, v);   // this warp's next own chunk, in flight during the reduction
+          if (cc + kEpiSub < cps) tmem_ld_32x32(t_row + (c + kEpiSub) * 32, v);   // this warp's next own chunk, in flight during the reduction
           for (int slot = 0; slot < S - 1; ++slot) {
             const uint8_t* src = smem_gen + (recv_base - smem_base) + ((slot * cps + cc) * 8 * kBM + row_in_tile) * 16;
 #pragma unroll
@@ -669,7 +673,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
           if (o != crank) mbar_arrive_remote(map_to_cta(recv_free_bar, o));
       }
       if (!kConv && p.stat_out && out_row >= 0)
-        p.stat_out[out_row * p.stat_parts + (tn * S + (S > 1 ? static_cast<int>(crank) : 0)) * 2 + half] = make_float2(stat.s, stat.q);
+        p.stat_out[out_row * p.stat_parts + (tn * S + (S > 1 ? static_cast<int>(crank) : 0)) * kEpiSub + half] = make_float2(stat.s, stat.q);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
@@ -962,7 +966,7 @@ extern "C" int bxl_gemm_fused_f16(const bxl_gemm_fused_args* a, int* row_stats_p
                                      g_force_pair < 0 ? kDefaultPair : g_force_pair, 0.0, ln ? kSmemLnExtra : 0);
   const int tiles_n = (N + tc.bn - 1) / tc.bn;
   if (a->row_stats) {
-    const long long parts = 2ll * tiles_n * (tc.pair ? 1 : tc.split);  // two epilogue warps per row and column slice
+    const long long parts = (long long)kEpiSub * tiles_n * (tc.pair ? 1 : tc.split);  // one per epilogue warp of a row and column slice
     if (a->row_stats_capacity < 2ll * M * parts)
       return fail(kErrTooLarge, "bxl_gemm_fused_f16: row statistics need %lld floats, %lld given", 2ll * M * parts, a->row_stats_capacity);
     *row_stats_parts = (int)parts;

@@ -152,7 +152,7 @@ class FoldedLayerNorm:
         self.eps = float(eps)
 
 
-_MAX_STAT_PARTS = 128
+_MAX_STAT_PARTS = 256
 
 
 def gemm_fused(a, w, *, bias=None, bias_f32=None, residual=None, out=None, out2=None, n_split=0, geglu=False,
@@ -192,7 +192,7 @@ def gemm_fused(a, w, *, bias=None, bias_f32=None, residual=None, out=None, out2=
         args.ln_colsum, args.ln_eps = _p(fold.colsum), fold.eps
     stats = None
     if want_stats:
-        buf = torch.empty((M, min(_MAX_STAT_PARTS, 2 * max(1, N // 32)), 2), device=a.device, dtype=torch.float32)
+        buf = torch.empty((M, min(_MAX_STAT_PARTS, 4 * max(1, N // 32)), 2), device=a.device, dtype=torch.float32)
         args.row_stats, args.row_stats_capacity = _p(buf), buf.numel()
     args.M, args.N, args.K = M, N, K
     parts = C.c_int(0)
