@@ -36,6 +36,8 @@
 // score, two warps per scheduler) needs more cycles per tile than the two matrix products;
 // measured, the kernel is bound by that instruction stream (evaluating part of the
 // exponentials with a polynomial on the FMA pipe made it slower).
+#include <stdlib.h>
+
 #include "bxl_common.cuh"
 #include "bxl_host.h"
 #include "../../include/basedxl_b200.h"
@@ -62,6 +64,7 @@ struct alignas(64) AttnParams {
   long long out_img_stride, ld_out;
   float scale_log2e;               // softmax scale * log2(e)
   int kv_split;                    // K/V range split over a cluster of 1, 2 or 4 CTAs
+  int n_full;                      // units [0, n_full) are whole (256 queries); each later unit is served as two halves of 128
   int* dev_status;
 };
 
@@ -206,13 +209,18 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
   const int S = p.kv_split;
   const uint32_t crank = (S > 1) ? cluster_ctarank() : 0u;
   const int q_pairs = (p.L_q + 2 * kTileQ - 1) / (2 * kTileQ);
-  const int units_total = q_pairs * p.heads * p.B;
+  // Units past n_full are the last, under-filled round of a persistent grid: each is served as two
+  // half units (one query tile) so that twice as many CTAs share that round.
+  const int n_full = p.n_full;
+  const int units_total = n_full + 2 * (q_pairs * p.heads * p.B - n_full);
   const int first_unit = (S > 1) ? static_cast<int>(blockIdx.x) / S : static_cast<int>(blockIdx.x);
   const int unit_step = (S > 1) ? units_total : static_cast<int>(gridDim.x);
-  auto unit_q_row0 = [&](int w) { return (w % q_pairs) * 2 * kTileQ; };
-  auto unit_head = [&](int w) { return (w / q_pairs) % p.heads; };
-  auto unit_img = [&](int w) { return w / (q_pairs * p.heads); };
-  auto unit_groups = [&](int w) { return (unit_q_row0(w) + kTileQ < p.L_q) ? 2 : 1; };  // the second tile may lie wholly past L_q
+  auto unit_pair = [&](int w) { return w < n_full ? w : n_full + ((w - n_full) >> 1); };      // index of the 256-query block
+  auto unit_q_row0 = [&](int w) { return (unit_pair(w) % q_pairs) * 2 * kTileQ + ((w >= n_full && ((w - n_full) & 1)) ? kTileQ : 0); };
+  auto unit_head = [&](int w) { return (unit_pair(w) / q_pairs) % p.heads; };
+  auto unit_img = [&](int w) { return unit_pair(w) / (q_pairs * p.heads); };
+  // the second tile may lie wholly past L_q; a half unit has one tile
+  auto unit_groups = [&](int w) { return (w < n_full && unit_q_row0(w) + kTileQ < p.L_q) ? 2 : 1; };
   const int tiles_per_slot = (p.L_slot + kTileKV - 1) / kTileKV;
   const int total_tiles = p.n_slots * tiles_per_slot;
   const int tile0 = static_cast<int>((static_cast<long long>(crank) * total_tiles) / S);   // first K/V tile of this CTA
@@ -679,6 +687,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const __grid
 }
 
 static int g_force_attn_split = 0;  // test hook: 0 = choose
+static int g_attn_tail_split = 1;   // serve an under-filled last round as half units (BXL_ATTN_TAIL_SPLIT=0 turns it off)
 
 }  // namespace bxl
 
@@ -751,7 +760,20 @@ extern "C" int bxl_attn_fwd_f16(const void* q, long long q_img_stride, long long
     if (cost < best - 1e-9) best = cost, split = s2;
   }
   p.kv_split = split;
-  const int grid = (split == 1) ? (work < sm_count() ? work : sm_count()) : work * split;
+  // A persistent grid whose last round would keep at most half of the SMs busy serves that round's
+  // units as half units (one query tile each): twice the CTAs, about half the time.
+  p.n_full = work;
+  static int tail_env = -1;
+  if (tail_env < 0) {
+    const char* e = getenv("BXL_ATTN_TAIL_SPLIT");
+    tail_env = (e && e[0] == '0') ? 0 : 1;
+  }
+  if (split == 1 && g_attn_tail_split && tail_env && L_q % (2 * kTileQ) == 0 && work > sm_count()) {
+    const int rem = work % sm_count();
+    if (rem > 0 && 2 * rem <= sm_count()) p.n_full = work - rem;
+  }
+  const int units = p.n_full + 2 * (work - p.n_full);
+  const int grid = (split == 1) ? (units < sm_count() ? units : sm_count()) : work * split;
   return launch_kernel("attention_kernel launch", attention_kernel, dim3(grid), dim3(kAttnThreads), AttnSmem::kTotal,
                        (cudaStream_t)stream, split, p);
 }

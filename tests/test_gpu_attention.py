@@ -28,6 +28,8 @@ def _ops():
         (1, 2, 256, 128, 3),
         (2, 10, 77, 77, 1),       # ragged query and key tiles
         (2, 10, 512, 77, 1),      # cross-attention: 77 text tokens
+        (2, 20, 1024, 128, 2),    # 160 work units on 148 SMs: the under-filled second round runs as half units
+        (2, 20, 1024, 77, 1),     # the same count for cross-attention
         (1, 3, 200, 72, 4),       # ragged slots
         (2, 10, 512, 512, 8),     # benchmark shape at world size 8: L = 4096
         (2, 20, 256, 256, 4),     # 1280-level blocks, 4 strips
