@@ -15,10 +15,12 @@
 //               convert and store; runs while the next tile's mainloop fills the
 //               other accumulator buffer (two TMEM buffers of BN columns).  Nothing
 //               the epilogue needs from global memory is fetched on its critical
-//               path: the tile's bias row is staged in shared memory while the MMAs
-//               still run, the residual is fetched two 32-column chunks ahead, the
-//               accumulator load of the next chunk is in flight during the current
+//               path: the tile's bias row (and, with a folded LayerNorm, the weight
+//               column sums and the row's mean / rstd) is staged while the MMAs still
+//               run, the residual of a warp's next chunk is fetched during its current
 //               one, and a thread stores its 64 bytes of a chunk as two whole sectors.
+//               One accumulator chunk is loaded at a time: more loads in flight per
+//               warp measured slower, a second warp per scheduler faster.
 //
 // Tile width BN (32..256), an optional K split and CTA pairing are chosen per
 // problem by the host.  With a K split of S, the S CTAs of a thread-block cluster
