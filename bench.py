@@ -59,52 +59,108 @@ def load_peaks():
 
 # --------------------------------------------------------------------------- clocks
 class ClockSampler:
-    Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    """SM clock, power and clock-event reasons of one GPU, sampled while the timed region runs.
+    Reads through NVML every 20 ms from a thread of this process (read-only queries); falls back
+    to an `nvidia-smi -lms 50` child if the NVML binding is missing.  Only samples taken between
+    `mark_begin()` and `mark_end()` are reported."""
 
-    def __init__(self, gpu_index: int):
-        self.gpu_index = gpu_index
+    Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    REASON_BITS = (("sw_power_cap", 0x4), ("hw_slowdown", 0x8), ("sw_thermal_slowdown", 0x20), ("hw_thermal_slowdown", 0x40))
+
+    def __init__(self, device):
+        self.device = device
+        self.gpu_index = device.index if device.index is not None else 0
         self.proc = None
-        self.lines: list[str] = []
+        self.nvml = None
+        self.samples: list[tuple] = []   # (monotonic time, sm MHz, max MHz, watts, [reasons])
+        self.t_begin = self.t_end = None
+        self._stop = threading.Event()
+
+    def _nvml_handle(self):
+        import pynvml
+
+        pynvml.nvmlInit()
+        try:
+            uuid = str(torch.cuda.get_device_properties(self.device).uuid)
+            uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+            try:
+                h = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            except TypeError:
+                h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+        except Exception:
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
+        return pynvml, h
 
     def start(self):
         try:
+            self.nvml = self._nvml_handle()
+            self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
+        try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
             )
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread = threading.Thread(target=self._read_smi, daemon=True)
             self.thread.start()
         except Exception:
             self.proc = None
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+    def _poll_nvml(self):
+        nv, h = self.nvml
+        mx = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+        reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self._stop.is_set():
+            try:
+                sm = float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                watts = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+                mask = int(reasons_fn(h))
+                self.samples.append((time.monotonic(), sm, mx, watts, [n for n, bit in self.REASON_BITS if mask & bit]))
+            except Exception:
+                pass
+            self._stop.wait(0.02)
 
-    def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        sm, mx, reasons, power = [], [], set(), []
-        for ln in self.lines:
-            f = [x.strip() for x in ln.split(",")]
+    def _read_smi(self):
+        for line in self.proc.stdout:
+            f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+                sm, mx, watts = float(f[1]), float(f[2]), float(f[3])
             except ValueError:
                 continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
+            names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+            self.samples.append((time.monotonic(), sm, mx, watts, [n for n, v in zip(names, f[5:9]) if v.lower().startswith("active")]))
+
+    def mark_begin(self):
+        self.t_begin = time.monotonic()
+
+    def mark_end(self):
+        self.t_end = time.monotonic()
+
+    def stop(self) -> dict:
+        self._stop.set()
+        if self.nvml is None and self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock source (NVML binding and nvidia-smi unavailable)"]}
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+        else:
+            self.thread.join(timeout=1.0)
+        lo = self.t_begin if self.t_begin is not None else -1e30
+        hi = self.t_end if self.t_end is not None else 1e30
+        inside = [x for x in self.samples if lo <= x[0] <= hi]
+        if not inside:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
-                "power_w_max": max(power), "samples": len(sm)}
+        reasons = sorted({r for x in inside for r in x[4]})
+        return {"sm_mhz": statistics.median(x[1] for x in inside), "sm_max_mhz": max(x[2] for x in inside), "reasons": reasons,
+                "power_w_max": max(x[3] for x in inside), "samples": len(inside), "source": "nvml" if self.nvml else "nvidia-smi"}
 
 
 # --------------------------------------------------------------------------- synthetic inputs
@@ -523,10 +579,12 @@ def run_b200_arm(args):
     if world > 1:
         warm_steps = max(warm_steps, args.steps, cfg.warmup_steps + 2)
     pipe.denoise(lat, ehs, added, steps_total, 5.0, first_step=0, last_step=min(warm_steps, steps_total))
-    barrier()
-    sampler = ClockSampler(dev.index if dev.index is not None else 0)
+    sampler = ClockSampler(dev)
     sampler.start()
+    barrier()
+    sampler.mark_begin()
     ms_total, launches, out = timed_image(lat, ehs, added)
+    sampler.mark_end()
     clocks = sampler.stop()
     ms_second, _, out2 = timed_image(lat, ehs, added)
     # per-step device times of one more image (diagnostic: synchronous vs displaced steps)
