@@ -35,6 +35,7 @@ SIGNATURES = {
     "bxl_set_pdl": (_i, [_i]),
     "bxl_set_static_weights": (_i, [_i]),
     "bxl_debug_force_tiles": (_i, [_i, _i, _i]),
+    "bxl_debug_force_tile_order": (_i, [_i]),
     "bxl_debug_force_attn_split": (_i, [_i]),
     "bxl_gemm_f16": (_i, [_vp, _ll, _vp, _ll, _i, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _vp]),
     "bxl_gemm_dual_f16": (_i, [_vp, _ll, _vp, _ll, _vp, _vp, _ll, _i, _vp, _ll, _i, _i, _i, _vp]),

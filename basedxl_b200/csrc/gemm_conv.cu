@@ -74,6 +74,7 @@ struct alignas(64) GemmParams {
   int pair;                    // CTA pairs (cta_group::2): 256-row tiles, each CTA stages half of B (split == 1)
   int stages;                  // depth of the operand ring
   int b_static;                // B (weights) is not written by the preceding kernel: its copies start before the grid dependency wait
+  int n_fastest;               // tile order: 0 = consecutive tiles walk M (they share a B tile), 1 = they walk N (they share an A tile)
   // epilogue
   const __half* bias;          // [N] or null
   const __half* bias_rows;     // conv only: [B][N] per-image bias (time embedding) or null
@@ -347,8 +348,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
-        const int tm = (tile % tiles_m) * kWidth + (kPair ? static_cast<int>(crank) : 0);  // this CTA's 128-row tile
-        const int tn = tile / tiles_m;
+        const int tm = (p.n_fastest ? tile / tiles_n : tile % tiles_m) * kWidth + (kPair ? static_cast<int>(crank) : 0);  // this CTA's 128-row tile
+        const int tn = p.n_fastest ? tile % tiles_n : tile / tiles_m;
         const int n0 = tn * BN + (kPair ? static_cast<int>(crank) * b_rows : 0);           // first B row this CTA stages
         int img = 0, y0 = 0, x0 = 0;
         if (kConv) {
@@ -524,8 +525,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_conv_kernel(const __grid
     for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
-      const int tm = (tile % tiles_m) * kWidth + (kPair ? static_cast<int>(crank) : 0);
-      const int tn = tile / tiles_m;
+      const int tm = (p.n_fastest ? tile / tiles_n : tile % tiles_m) * kWidth + (kPair ? static_cast<int>(crank) : 0);
+      const int tn = p.n_fastest ? tile % tiles_n : tile / tiles_m;
       const int n0 = tn * BN;
       long long out_row = -1;  // row index into C / residual, -1 = not stored
       int img = 0;
@@ -804,6 +805,7 @@ static int aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 1
 constexpr int kDefaultPair = -1;  // -1 = let the cost model decide
 constexpr double kConvAMinUs = 0.36;  // per-k-block floor of the convolution's image copies
 static int g_force_bn = 0, g_force_split = 0, g_force_pair = -1;
+static int g_force_order = -1;  // -1 = choose, 0 = consecutive tiles walk M, 1 = they walk N
 
 }  // namespace bxl
 
@@ -1015,6 +1017,12 @@ extern "C" int bxl_debug_force_tiles(int bn, int split, int pair) {
   return kOk;
 }
 
+extern "C" int bxl_debug_force_tile_order(int order) {
+  if (order < -1 || order > 1) return fail(kErrInvalidArg, "bxl_debug_force_tile_order: -1 (choose), 0 (walk M first) or 1 (walk N first)");
+  g_force_order = order;
+  return kOk;
+}
+
 // ---- split-operand product of fp32 matrices ---------------------------------------
 namespace bxl {
 // x = hi + lo with hi = fp16(x), lo = fp16(x - hi): 22 significant bits kept.
@@ -1174,6 +1182,11 @@ extern "C" int bxl_conv3x3_halo_f16(const void* x, long long x_img_stride, const
   p.tw = tw, p.th = th;
   p.tiles_x = tiles_x, p.tiles_y = tiles_y;
   p.has_top = top ? 1 : 0, p.has_bot = bot ? 1 : 0;
+  // An input that does not stay in L2 while the output streams through it is walked once: the CTAs
+  // running at the same time then take the column tiles of the same pixels (the packed weights,
+  // a few MB, stay resident instead).
+  p.n_fastest = (C_out > BN && 2ll * B * H_in * W * C_in > (48ll << 20)) ? 1 : 0;
+  if (g_force_order >= 0) p.n_fastest = g_force_order;
   p.dev_status = st;
   return launch<true>(p, B * tiles_x * tiles_y, (C_out + BN - 1) / BN, (cudaStream_t)stream);
 }

@@ -58,6 +58,12 @@ int bxl_set_static_weights(int enabled);
  * restore the built-in choice.  No counterpart in the reference. */
 int bxl_debug_force_tiles(int bn, int split, int pair);
 
+/* Test hook: force the order in which the convolution's output tiles are handed to the CTAs:
+ * 0 = consecutive tiles walk the pixels (they share a weight tile), 1 = they walk the output
+ * channels (they share an input tile; chosen by itself when the input exceeds what stays in
+ * L2), -1 restores the built-in choice.  No counterpart in the reference. */
+int bxl_debug_force_tile_order(int order);
+
 /* Test hook: force the K/V split of the attention kernel (1, 2 or 4 CTAs per query block;
  * 0 restores the built-in choice).  No counterpart in the reference. */
 int bxl_debug_force_attn_split(int split);

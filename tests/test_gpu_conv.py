@@ -201,6 +201,46 @@ def test_conv_forced_tile_width_and_k_split(bn, split, pair):
         _lib.check(l.bxl_debug_force_tiles(0, 0, -1), l, kernels=0)
 
 
+@pytest.mark.parametrize("order", [0, 1])
+@pytest.mark.parametrize("bn,split,pair", [(64, 1, 0), (128, 2, 0), (128, 1, 1)])
+def test_conv_tile_order(order, bn, split, pair):
+    """Both orders in which output tiles are handed to the CTAs (pixels first / output channels
+    first, the latter chosen by the library for inputs that do not stay in L2) give the same
+    result, with several column tiles per pixel tile, a K split and a CTA pair."""
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    gen = torch.Generator().manual_seed(7 + bn)
+    x = h16(torch.randn(3, 64, 24, 40, generator=gen))
+    w = h16(torch.randn(320, 64, 3, 3, generator=gen) / 24)
+    b = h16(torch.randn(320, generator=gen))
+    ref = po.conv2d_pp(x, w, b, 1, 1, None, 0, 1)
+    l = _lib.lib()
+    _lib.check(l.bxl_debug_force_tiles(bn, split, pair), l, kernels=0)
+    _lib.check(l.bxl_debug_force_tile_order(order), l, kernels=0)
+    try:
+        y = _conv(ops, dev, x, w, b, 1, None, None)
+        _lib.device_status()
+        assert_close(y, ref, what=f"conv order={order} bn={bn} split={split} pair={pair}")
+    finally:
+        _lib.check(l.bxl_debug_force_tiles(0, 0, -1), l, kernels=0)
+        _lib.check(l.bxl_debug_force_tile_order(-1), l, kernels=0)
+
+
+def test_conv_input_larger_than_l2():
+    """63 MB of input (more than stays in L2 beside the output): the library hands out the tiles
+    output channels first; result against the oracle."""
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    gen = torch.Generator().manual_seed(11)
+    x = h16(torch.randn(2, 320, 192, 256, generator=gen))
+    w = h16(torch.randn(320, 320, 3, 3, generator=gen) / 54)
+    b = h16(torch.randn(320, generator=gen))
+    ref = po.conv2d_pp(x, w, b, 1, 1, None, 0, 1)
+    y = _conv(ops, dev, x, w, b, 1, None, None)
+    _lib.device_status()
+    assert_close(y, ref, what="conv 320->320 192x256, tiles handed out channels first")
+
+
 @pytest.mark.parametrize("n", [1, 2, 4, 8])
 def test_auto_tiling_on_every_per_rank_conv_shape(n):
     """The 3x3 convolutions of the UNet on the strips a rank sees when the image is split
