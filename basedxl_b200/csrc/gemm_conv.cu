@@ -806,6 +806,12 @@ constexpr int kDefaultPair = -1;  // -1 = let the cost model decide
 constexpr double kConvAMinUs = 0.36;  // per-k-block floor of the convolution's image copies
 static int g_force_bn = 0, g_force_split = 0, g_force_pair = -1;
 static int g_force_order = -1;  // -1 = choose, 0 = consecutive tiles walk M, 1 = they walk N
+// Linear layers: an activation matrix that does not stay in L2 beside the output is walked once
+// (the CTAs running at one time take the column tiles of the same rows) as long as the weights do.
+static int linear_tile_order(long long M, long long N, long long K, int bn) {
+  if (g_force_order >= 0) return g_force_order;
+  return (N > bn && 2 * M * K > (48ll << 20) && 2 * N * K < (32ll << 20)) ? 1 : 0;
+}
 
 }  // namespace bxl
 
@@ -852,6 +858,7 @@ extern "C" int bxl_gemm_f16(const void* A, long long lda, const void* B, long lo
   }
   p.M = M, p.N = N, p.K = K, p.nseg = 1, p.b_kn = b_is_kn ? 1 : 0;
   p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair, p.b_static = static_weights() ? 1 : 0;
+  p.n_fastest = linear_tile_order(M, N, K, tc.bn);
   p.bias = static_cast<const __half*>(bias);
   p.residual = static_cast<const __half*>(residual);
   p.ldr = ldr, p.C = C, p.ldc = ldc, p.out_f32 = out_f32 ? 1 : 0;
@@ -892,6 +899,7 @@ extern "C" int bxl_gemm_dual_f16(const void* A, long long lda, const void* B, lo
   }
   p.M = M, p.N = N, p.K = K, p.nseg = 1, p.b_kn = 0;
   p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair, p.b_static = static_weights() ? 1 : 0;
+  p.n_fastest = linear_tile_order(M, N, K, tc.bn);
   p.bias = static_cast<const __half*>(bias);
   p.C = C1, p.ldc = ldc1, p.C2 = C2, p.ldc2 = ldc2, p.n_split = n1;
   p.dev_status = st;
@@ -929,6 +937,7 @@ extern "C" int bxl_gemm_geglu_f16(const void* A, long long lda, const void* B, l
   }
   p.M = M, p.N = N, p.K = K, p.nseg = 1, p.b_kn = 0;
   p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair, p.b_static = static_weights() ? 1 : 0;
+  p.n_fastest = linear_tile_order(M, N, K, tc.bn);
   p.bias = static_cast<const __half*>(bias);
   p.C = C, p.ldc = ldc, p.out_f32 = 0, p.geglu = 1;
   p.dev_status = st;
@@ -995,6 +1004,7 @@ extern "C" int bxl_gemm_fused_f16(const bxl_gemm_fused_args* a, int* row_stats_p
   }
   p.M = M, p.N = N, p.K = K, p.nseg = 1, p.b_kn = 0;
   p.bn = tc.bn, p.split = tc.split, p.stages = tc.stages, p.pair = tc.pair, p.b_static = static_weights() ? 1 : 0;
+  p.n_fastest = linear_tile_order(M, N, K, tc.bn);
   p.bias = static_cast<const __half*>(a->bias);
   p.bias_f32 = a->bias_f32;
   p.residual = static_cast<const __half*>(a->residual);

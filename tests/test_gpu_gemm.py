@@ -134,6 +134,36 @@ def test_forced_tile_width_and_k_split(M, K, N, b_is_kn, bn, split):
     assert_close(y, ref, what=f"gemm bn={bn} split={split}")
 
 
+@pytest.mark.parametrize("order", [0, 1])
+@pytest.mark.parametrize("bn,split", [(64, 1), (128, 2), (256, 1)])
+def test_gemm_tile_order(order, bn, split):
+    """Both orders in which output tiles are handed to the CTAs (rows first / columns first, the
+    latter chosen by the library for activations that do not stay in L2) give the same result,
+    row statistics of the output included."""
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    g = torch.Generator().manual_seed(5 + bn + split)
+    M, K, N = 640, 320, 768
+    a = torch.randn(M, K, generator=g)
+    w = torch.randn(N, K, generator=g) / K**0.5
+    bias = torch.randn(N, generator=g)
+    ref = h16(a) @ h16(w).t() + h16(bias)
+    l = _lib.lib()
+    _lib.check(l.bxl_debug_force_tiles(bn, split, -1), l, kernels=0)
+    _lib.check(l.bxl_debug_force_tile_order(order), l, kernels=0)
+    try:
+        y = ops.gemm(a.half().to(dev), w.half().to(dev), bias=bias.half().to(dev))
+        y2, stats = ops.gemm_fused(a.half().to(dev), w.half().to(dev), bias=bias.half().to(dev), want_stats=True)
+        _lib.device_status()
+    finally:
+        _lib.check(l.bxl_debug_force_tiles(0, 0, -1), l, kernels=0)
+        _lib.check(l.bxl_debug_force_tile_order(-1), l, kernels=0)
+    assert_close(y, ref, what=f"gemm order={order} bn={bn} split={split}")
+    assert torch.equal(y, y2)
+    mean, _ = stats.moments(N)
+    assert_close(mean, y.float().cpu().mean(dim=1), tol=1e-4, what="row mean of the stored values")
+
+
 @pytest.mark.parametrize("tokens", [8192, 4096, 2048, 1024, 512, 256])
 def test_auto_tiling_on_every_per_rank_linear_shape(tokens):
     """The linear-layer shapes of the UNet at the token counts a rank sees with 1, 2, 4
