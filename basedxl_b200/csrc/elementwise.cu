@@ -84,6 +84,88 @@ __global__ void conv3x3_small_cin_kernel(const __half* __restrict__ x, long long
   }
 }
 
+// The same for C_in == 4 (the latent input of the UNet): a thread computes FOUR consecutive
+// pixels of a row for its 8 output channels, so every weight vector fetched from shared memory
+// serves four pixels (the one-pixel form above is bound by those fetches), and the 3 x 6 input
+// pixels it needs are read once as 8-byte vectors.
+__global__ void __launch_bounds__(256) conv3x3_cin4_kernel(const __half* __restrict__ x, long long x_img_stride,
+                                                          const __half* __restrict__ top, const __half* __restrict__ bot,
+                                                          long long halo_img_stride, const __half* __restrict__ w,
+                                                          const __half* __restrict__ bias, __half* __restrict__ y, int B,
+                                                          int Cout, int H, int W) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float s_w[];  // [36][Cout]
+  constexpr int K = 36;
+  for (int i = threadIdx.x; i < Cout * K; i += blockDim.x) s_w[(i % K) * Cout + i / K] = __half2float(w[i]);
+  __syncthreads();
+  const int ovecs = Cout / 8;
+  const int wq = (W + 3) / 4;  // groups of four pixels per row
+  const long long total = (long long)B * H * wq * ovecs;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int ov = i % ovecs;
+    const long long grp = i / ovecs;
+    const int ox0 = static_cast<int>(grp % wq) * 4;
+    const int oy = static_cast<int>((grp / wq) % H);
+    const int img = static_cast<int>(grp / ((long long)wq * H));
+    float acc[4][8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float b = bias ? __half2float(bias[ov * 8 + j]) : 0.f;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[q][j] = b;
+    }
+#pragma unroll
+    for (int ky = 0; ky < 3; ++ky) {
+      const int iy = oy + ky - 1;
+      const __half* rowp = nullptr;
+      if (iy < 0) {
+        if (top) rowp = top + (long long)img * halo_img_stride;
+      } else if (iy >= H) {
+        if (bot) rowp = bot + (long long)img * halo_img_stride;
+      } else {
+        rowp = x + (long long)img * x_img_stride + (long long)iy * W * 4;
+      }
+      if (!rowp) continue;
+      float v[6][4];  // input pixels ox0-1 .. ox0+4, zero outside the row
+#pragma unroll
+      for (int t = 0; t < 6; ++t) {
+        const int ix = ox0 + t - 1;
+        uint2 u = make_uint2(0u, 0u);
+        if (ix >= 0 && ix < W) u = *reinterpret_cast<const uint2*>(rowp + (long long)ix * 4);
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+        v[t][0] = a.x, v[t][1] = a.y, v[t][2] = b.x, v[t][3] = b.y;
+      }
+#pragma unroll
+      for (int kx = 0; kx < 3; ++kx) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float* wp = &s_w[((ky * 3 + kx) * 4 + c) * Cout + ov * 8];
+          const float4 w0 = *reinterpret_cast<const float4*>(wp), w1 = *reinterpret_cast<const float4*>(wp + 4);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float a = v[q + kx][c];
+            acc[q][0] = fmaf(a, w0.x, acc[q][0]), acc[q][1] = fmaf(a, w0.y, acc[q][1]);
+            acc[q][2] = fmaf(a, w0.z, acc[q][2]), acc[q][3] = fmaf(a, w0.w, acc[q][3]);
+            acc[q][4] = fmaf(a, w1.x, acc[q][4]), acc[q][5] = fmaf(a, w1.y, acc[q][5]);
+            acc[q][6] = fmaf(a, w1.z, acc[q][6]), acc[q][7] = fmaf(a, w1.w, acc[q][7]);
+          }
+        }
+      }
+    }
+    const long long pix0 = ((long long)img * H + oy) * W + ox0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if (ox0 + q >= W) break;
+      uint4 o;
+      __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) oh[j] = __floats2half2_rn(acc[q][2 * j], acc[q][2 * j + 1]);
+      *reinterpret_cast<uint4*>(y + (pix0 + q) * Cout + ov * 8) = o;
+    }
+  }
+}
+
 // ---- direct 3x3 conv, few output channels (conv_out) ----------------------------
 // one warp per output pixel; lanes stride over 16-byte input vectors of the 9 taps.
 template <int COUT>
@@ -331,6 +413,25 @@ extern "C" int bxl_conv3x3_direct_f16(const void* x, long long x_img_stride, con
                               "cudaFuncSetAttribute(conv_small_cin)"))
         return rc;
       configured[dev] = true;
+    }
+    // C_in == 4 with 8-byte aligned rows: four pixels per thread
+    if (C_in == 4 && x_img_stride % 4 == 0 && halo_img_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 7u) == 0 &&
+        (!top || (reinterpret_cast<uintptr_t>(top) & 7u) == 0) && (!bot || (reinterpret_cast<uintptr_t>(bot) & 7u) == 0) && al16(y)) {
+      static bool configured4[64] = {};
+      if (dev >= 0 && dev < 64 && !configured4[dev]) {
+        if (int rc = check_cuda(cudaFuncSetAttribute(conv3x3_cin4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024),
+                                "cudaFuncSetAttribute(conv_cin4)"))
+          return rc;
+        configured4[dev] = true;
+      }
+      const long long total4 = (long long)B * H * ((W + 3) / 4) * (C_out / 8);
+      int blocks4 = grid_for(total4, 256);
+      if (blocks4 > sm_count() * 4) blocks4 = sm_count() * 4;  // weights are staged once per CTA
+      conv3x3_cin4_kernel<<<blocks4, 256, smem, s>>>(static_cast<const __half*>(x), x_img_stride, static_cast<const __half*>(top),
+                                                     static_cast<const __half*>(bot), halo_img_stride,
+                                                     static_cast<const __half*>(w_packed), static_cast<const __half*>(bias),
+                                                     static_cast<__half*>(y), B, C_out, H, W);
+      return check_cuda(cudaGetLastError(), "conv3x3_cin4 launch");
     }
     const long long total = (long long)B * H * W * (C_out / 8);
     int blocks = grid_for(total, 256);

@@ -1135,7 +1135,7 @@ extern "C" int bxl_conv3x3_halo_f16(const void* x, long long x_img_stride, const
   if (B <= 0 || H_in <= 0 || W <= 0) return fail(kErrInvalidArg, "bxl_conv3x3_halo_f16: non-positive extent");
   if (stride != 1 && stride != 2) return fail(kErrUnsupported, "bxl_conv3x3_halo_f16: stride %d (1 or 2 supported)", stride);
   if (C_in % 64) return fail(kErrUnsupported, "bxl_conv3x3_halo_f16: C_in=%d must be a multiple of 64 (use the direct kernel)", C_in);
-  if (C_out % 8) return fail(kErrUnsupported, "bxl_conv3x3_halo_f16: C_out=%d must be a multiple of 8", C_out);
+  if (C_out % 4) return fail(kErrUnsupported, "bxl_conv3x3_halo_f16: C_out=%d must be a multiple of 4", C_out);
   if (W % stride || H_in % stride) return fail(kErrInvalidArg, "bxl_conv3x3_halo_f16: H and W must be multiples of the stride");
   if (!aligned16(x) || !aligned16(w_packed) || !aligned16(y) || (top && !aligned16(top)) || (bot && !aligned16(bot)) ||
       (residual && !aligned16(residual)))

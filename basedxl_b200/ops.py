@@ -270,7 +270,7 @@ def conv3x3(x, w_packed, bias=None, stride=1, top=None, bot=None, bias_rows=None
              "conv3x3: bias_rows must be fp16 [B,C_out] with unit column stride")
         bias_rows_stride = bias_rows.stride(0) if B > 1 else Co
     l = _lib.lib()
-    if Ci % 64 == 0 and Co % 8 == 0:
+    if Ci % 64 == 0 and Co % 4 == 0:
         _lib.check(
             l.bxl_conv3x3_halo_f16(
                 _p(x), x.stride(0), _p(top), _p(bot), halo_stride, _p(w_packed), _p(bias), _p(bias_rows), bias_rows_stride,

@@ -154,7 +154,8 @@ int bxl_conv_weight_pack_f16(const void* w_oihw, void* w_packed, int c_out, int 
  * y[B,H_in/stride,W/stride,C_out] (+ bias[C_out]) (+ bias_rows[B,C_out], rows
  * bias_rows_stride elements apart, 0 = C_out: a slice of a wider matrix that holds the
  * time-embedding projections of several layers) (+ residual, same shape as y).
- * Implicit GEMM on tcgen05; C_in % 64 == 0.
+ * Implicit GEMM on tcgen05; C_in % 64 == 0, C_out % 4 == 0 (the last convolution of the
+ * network, 320 -> 4, runs here on a 32-wide tile whose unused weight rows are zero fill).
  * Replaces: BasedConv2dPP.forward's padded-input assembly and F.conv2d
  * (basedxl/modules/conv2d.py:74-104) and naive_forward (:15-18). */
 int bxl_conv3x3_halo_f16(const void* x, long long x_img_stride, const void* top, const void* bot,
@@ -163,9 +164,10 @@ int bxl_conv3x3_halo_f16(const void* x, long long x_img_stride, const void* top,
                          int W, int stride, void* stream);
 
 /* Same contract, stride 1, for the two thin convolutions at the ends of the
- * network (C_in <= 16, or C_out == 4): direct CUDA-core kernels.
+ * network (C_in <= 16, or C_out == 4 with C_in % 64 != 0): direct CUDA-core kernels
+ * (C_in == 4: four pixels per thread).
  * Replaces: BasedConv2dPP.sliced_forward (basedxl/modules/conv2d.py:20-41) for
- * conv_in, and the forward above for conv_out. */
+ * conv_in, and the forward above for a thin conv_out. */
 int bxl_conv3x3_direct_f16(const void* x, long long x_img_stride, const void* top, const void* bot,
                            long long halo_img_stride, const void* w_packed, const void* bias, void* y, int B, int C_in,
                            int C_out, int H, int W, void* stream);

@@ -164,6 +164,35 @@ def test_direct_convs_at_network_ends(n):
         assert_close(y, ref, what=f"conv_out strip {i}/{n}")
 
 
+@pytest.mark.parametrize("W", [30, 36, 5])
+def test_conv_in_ragged_width(W):
+    """conv_in on widths that are not a multiple of the four pixels a thread computes."""
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    gen = torch.Generator().manual_seed(W)
+    x = h16(torch.randn(2, 4, 12, W, generator=gen))
+    w = h16(torch.randn(320, 4, 3, 3, generator=gen) / 6)
+    b = h16(torch.randn(320, generator=gen))
+    ref = torch.nn.functional.conv2d(x, w, b, padding=1)
+    y = _conv(ops, dev, x, w, b, 1, None, None)
+    _lib.device_status()
+    assert_close(y, ref, what=f"conv_in W={W}")
+
+
+def test_thin_conv_out_off_the_tensor_path():
+    """A 4-channel output convolution whose C_in is not a multiple of 64 stays on the direct kernel."""
+    dev = cuda_or_skip()
+    _lib, ops = _ops()
+    gen = torch.Generator().manual_seed(3)
+    x = h16(torch.randn(2, 72, 16, 24, generator=gen))
+    w = h16(torch.randn(4, 72, 3, 3, generator=gen) / 25)
+    b = h16(torch.randn(4, generator=gen))
+    ref = torch.nn.functional.conv2d(x, w, b, padding=1)
+    y = _conv(ops, dev, x, w, b, 1, None, None)
+    _lib.device_status()
+    assert_close(y, ref, what="conv 72 -> 4")
+
+
 def test_halo_pack_is_bit_exact():
     dev = cuda_or_skip()
     _lib, ops = _ops()
