@@ -95,11 +95,38 @@ __global__ void __launch_bounds__(256) conv3x3_cin4_kernel(const __half* __restr
                                                           int Cout, int H, int W) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float s_w[];  // [36][Cout]
+  // weights as fp32, [36 taps x channels][2 halves][Cout / 8][4]: the threads of a warp (consecutive
+  // output vectors) read consecutive 16-byte words, first the lower four channels, then the upper four
+  extern __shared__ float s_w[];
   constexpr int K = 36;
-  for (int i = threadIdx.x; i < Cout * K; i += blockDim.x) s_w[(i % K) * Cout + i / K] = __half2float(w[i]);
-  __syncthreads();
   const int ovecs = Cout / 8;
+  {
+    // 16-byte loads, eight in flight per thread (one load per element made this loop, not the
+    // convolution, the longest part of the kernel)
+    const int nvec = Cout * K / 8;  // Cout is a multiple of 8
+    const uint4* wv = reinterpret_cast<const uint4*>(w);
+    for (int base = threadIdx.x; base < nvec; base += 8 * blockDim.x) {
+      uint4 buf[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int vi = base + j * blockDim.x;
+        buf[j] = vi < nvec ? wv[vi] : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int vi = base + j * blockDim.x;
+        if (vi >= nvec) continue;
+        const __half* hv = reinterpret_cast<const __half*>(&buf[j]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int i = vi * 8 + e;
+          const int o = i / K, k = i % K;
+          s_w[((k * 2 + ((o >> 2) & 1)) * ovecs + (o >> 3)) * 4 + (o & 3)] = __half2float(hv[e]);
+        }
+      }
+    }
+  }
+  __syncthreads();
   const int wq = (W + 3) / 4;  // groups of four pixels per row
   const long long total = (long long)B * H * wq * ovecs;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -140,8 +167,8 @@ __global__ void __launch_bounds__(256) conv3x3_cin4_kernel(const __half* __restr
       for (int kx = 0; kx < 3; ++kx) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          const float* wp = &s_w[((ky * 3 + kx) * 4 + c) * Cout + ov * 8];
-          const float4 w0 = *reinterpret_cast<const float4*>(wp), w1 = *reinterpret_cast<const float4*>(wp + 4);
+          const float* wp = &s_w[((((ky * 3 + kx) * 4 + c) * 2) * ovecs + ov) * 4];
+          const float4 w0 = *reinterpret_cast<const float4*>(wp), w1 = *reinterpret_cast<const float4*>(wp + ovecs * 4);
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const float a = v[q + kx][c];
@@ -415,7 +442,7 @@ extern "C" int bxl_conv3x3_direct_f16(const void* x, long long x_img_stride, con
       configured[dev] = true;
     }
     // C_in == 4 with 8-byte aligned rows: four pixels per thread
-    if (C_in == 4 && x_img_stride % 4 == 0 && halo_img_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 7u) == 0 &&
+    if (C_in == 4 && al16(w_packed) && x_img_stride % 4 == 0 && halo_img_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 7u) == 0 &&
         (!top || (reinterpret_cast<uintptr_t>(top) & 7u) == 0) && (!bot || (reinterpret_cast<uintptr_t>(bot) & 7u) == 0) && al16(y)) {
       static bool configured4[64] = {};
       if (dev >= 0 && dev < 64 && !configured4[dev]) {
